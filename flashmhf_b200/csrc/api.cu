@@ -1,0 +1,239 @@
+// C-ABI layer: argument validation, dispatch to the kernel families, status word, error text.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+#include "kernels.h"
+
+namespace fmhf {
+
+// One status word per device.  Kernels set it (first failure wins) when a bounded wait runs out.
+static __device__ int g_status_word;
+
+namespace {
+std::atomic<uint64_t> g_launches{0};
+thread_local char tl_cuda_error[256] = "";
+constexpr int kMaxDevices = 64;
+std::mutex g_mu;
+int *g_status_addr[kMaxDevices] = {nullptr};
+}  // namespace
+
+namespace {
+struct Profile {
+    bool on = false;
+    std::vector<cudaEvent_t> ev;
+    std::vector<int> tag;
+    size_t n = 0;
+};
+Profile g_prof;
+}  // namespace
+
+void prof_mark(cudaStream_t st, int tag) {
+    if (!g_prof.on) return;
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_prof.on || g_prof.n >= g_prof.ev.size()) return;
+    if (cudaEventRecord(g_prof.ev[g_prof.n], st) == cudaSuccess) g_prof.tag[g_prof.n++] = tag;
+}
+
+void set_cuda_error(cudaError_t e, const char *where) {
+    snprintf(tl_cuda_error, sizeof(tl_cuda_error), "%s: %s", where, cudaGetErrorString(e));
+}
+
+int *device_status_ptr() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_status_addr[dev]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+        g_status_addr[dev] = static_cast<int *>(p);
+    }
+    return g_status_addr[dev];
+}
+
+namespace {
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_dims(const flashmhf_dims &d) {
+    if (d.dtype != FLASHMHF_BF16 && d.dtype != FLASHMHF_F32_CHECK) return FLASHMHF_ERR_BAD_DTYPE;
+    if (d.B < 1 || d.H < 1 || d.S < 1 || d.Hkuv < 1 || d.E < 1 || d.De < 1) return FLASHMHF_ERR_BAD_SHAPE;
+    if (d.H % d.Hkuv != 0) return FLASHMHF_ERR_BAD_SHAPE;
+    if (d.De % 64 != 0) return FLASHMHF_ERR_BAD_SHAPE;
+    if (d.Dh != 64 && d.Dh != 96 && d.Dh != 128) return FLASHMHF_ERR_BAD_SHAPE;
+    if ((long long)d.E * d.De > (1LL << 30) || d.B > 65535 || d.H > 65535) return FLASHMHF_ERR_BAD_SHAPE;
+    return FLASHMHF_OK;
+}
+
+int check_tensor(const flashmhf_tensor &t) {
+    if (!t.ptr) return FLASHMHF_ERR_NULL;
+    if (!aligned16(t.ptr)) return FLASHMHF_ERR_MISALIGNED;
+    for (int i = 0; i < 3; ++i)
+        if (t.stride[i] < 0) return FLASHMHF_ERR_BAD_STRIDE;
+    return FLASHMHF_OK;
+}
+
+int check_arch() {
+    int dev = 0, major = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) {
+        set_cuda_error(e, "device query");
+        return FLASHMHF_ERR_CUDA;
+    }
+    return major == 10 ? FLASHMHF_OK : FLASHMHF_ERR_ARCH;
+}
+
+}  // namespace
+}  // namespace fmhf
+
+using namespace fmhf;
+
+extern "C" {
+
+int flashmhf_abi_version(void) { return FLASHMHF_ABI_VERSION; }
+
+const char *flashmhf_strerror(int status) {
+    switch (status) {
+        case FLASHMHF_OK: return "ok";
+        case FLASHMHF_ERR_NULL: return "a required pointer is NULL";
+        case FLASHMHF_ERR_BAD_SHAPE:
+            return "unsupported shape (need d_h in {64,96,128}, d_e % 64 == 0, H % H_kuv == 0, all dims >= 1)";
+        case FLASHMHF_ERR_BAD_DTYPE: return "unsupported dtype (FLASHMHF_BF16 or FLASHMHF_F32_CHECK)";
+        case FLASHMHF_ERR_BAD_STRIDE:
+            return "stride not expressible (negative, not a multiple of 16 bytes, or E and d_e do not collapse)";
+        case FLASHMHF_ERR_MISALIGNED: return "base pointer not 16-byte aligned";
+        case FLASHMHF_ERR_WORKSPACE: return "workspace missing, misaligned or too small";
+        case FLASHMHF_ERR_ARCH: return "current device is not compute capability 10.x (B200)";
+        case FLASHMHF_ERR_CUDA: return "CUDA call failed (see flashmhf_last_cuda_error)";
+        case FLASHMHF_ERR_DEVICE_TIMEOUT: return "a kernel gave up on a bounded wait";
+        default: return "unknown status";
+    }
+}
+
+const char *flashmhf_last_cuda_error(void) { return tl_cuda_error; }
+
+uint64_t flashmhf_launch_count(void) { return g_launches.load(); }
+
+int flashmhf_forward(const flashmhf_fwd_params *p, void *stream) {
+    if (!p) return FLASHMHF_ERR_NULL;
+    int rc = check_dims(p->d);
+    if (rc) return rc;
+    const flashmhf_tensor *ts[] = {&p->Q, &p->K, &p->U, &p->V, &p->R, &p->O};
+    for (const flashmhf_tensor *t : ts)
+        if ((rc = check_tensor(*t)) != 0) return rc;
+    if ((rc = check_arch()) != 0) return rc;
+    if (!device_status_ptr()) return FLASHMHF_ERR_CUDA;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int n = 0;
+    if (p->d.dtype == FLASHMHF_F32_CHECK) {
+        cudaError_t e = simt_forward(*p, st, &n);
+        if (e != cudaSuccess) {
+            set_cuda_error(e, "check forward launch");
+            rc = FLASHMHF_ERR_CUDA;
+        }
+    } else {
+        rc = tc_forward(*p, st, &n);
+    }
+    g_launches += (uint64_t)n;
+    return rc;
+}
+
+size_t flashmhf_backward_workspace_bytes(const flashmhf_dims *d) {
+    if (!d || check_dims(*d) != 0) return 0;
+    if (d->dtype == FLASHMHF_F32_CHECK) return 0;
+    return tc_backward_workspace_bytes(*d);
+}
+
+int flashmhf_backward(const flashmhf_bwd_params *p, void *stream) {
+    if (!p) return FLASHMHF_ERR_NULL;
+    int rc = check_dims(p->d);
+    if (rc) return rc;
+    const flashmhf_tensor *ts[] = {&p->Q, &p->K, &p->U, &p->V, &p->R, &p->dO, &p->dQ, &p->dK, &p->dU, &p->dV, &p->dR};
+    for (const flashmhf_tensor *t : ts)
+        if ((rc = check_tensor(*t)) != 0) return rc;
+    const size_t need = flashmhf_backward_workspace_bytes(&p->d);
+    if (need > 0 && (!p->workspace || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255u)))
+        return FLASHMHF_ERR_WORKSPACE;
+    if ((rc = check_arch()) != 0) return rc;
+    if (!device_status_ptr()) return FLASHMHF_ERR_CUDA;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int n = 0;
+    if (p->d.dtype == FLASHMHF_F32_CHECK) {
+        cudaError_t e = simt_backward(*p, st, &n);
+        if (e != cudaSuccess) {
+            set_cuda_error(e, "check backward launch");
+            rc = FLASHMHF_ERR_CUDA;
+        }
+    } else {
+        rc = tc_backward(*p, st, &n);
+    }
+    g_launches += (uint64_t)n;
+    return rc;
+}
+
+int flashmhf_profile_begin(int max_marks) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_prof.on || max_marks < 2) return FLASHMHF_ERR_BAD_SHAPE;
+    g_prof.ev.resize((size_t)max_marks);
+    g_prof.tag.assign((size_t)max_marks, 0);
+    for (int i = 0; i < max_marks; ++i) {
+        cudaError_t e = cudaEventCreate(&g_prof.ev[i]);
+        if (e != cudaSuccess) {
+            for (int j = 0; j < i; ++j) cudaEventDestroy(g_prof.ev[j]);
+            g_prof.ev.clear();
+            set_cuda_error(e, "cudaEventCreate");
+            return FLASHMHF_ERR_CUDA;
+        }
+    }
+    g_prof.n = 0;
+    g_prof.on = true;
+    return FLASHMHF_OK;
+}
+
+int flashmhf_profile_end(float *ms, int *tags, int capacity, int *n_out) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_prof.on) return FLASHMHF_ERR_BAD_SHAPE;
+    g_prof.on = false;
+    int n = 0, rc = FLASHMHF_OK;
+    cudaError_t e = cudaDeviceSynchronize();
+    for (size_t i = 1; e == cudaSuccess && i < g_prof.n; ++i) {
+        if (g_prof.tag[i] == kMarkStart) continue;  // interval between two calls, not a kernel
+        float t = 0.f;
+        e = cudaEventElapsedTime(&t, g_prof.ev[i - 1], g_prof.ev[i]);
+        if (e == cudaSuccess && ms && tags && n < capacity) {
+            ms[n] = t;
+            tags[n] = g_prof.tag[i];
+            ++n;
+        }
+    }
+    if (e != cudaSuccess) {
+        set_cuda_error(e, "flashmhf_profile_end");
+        rc = FLASHMHF_ERR_CUDA;
+    }
+    for (cudaEvent_t ev : g_prof.ev) cudaEventDestroy(ev);
+    g_prof.ev.clear();
+    g_prof.n = 0;
+    if (n_out) *n_out = n;
+    return rc;
+}
+
+int flashmhf_device_status(int *code) {
+    if (code) *code = 0;
+    int *addr = device_status_ptr();
+    if (!addr) return FLASHMHF_ERR_CUDA;
+    cudaError_t e = cudaDeviceSynchronize();
+    int v = 0;
+    if (e == cudaSuccess) e = cudaMemcpy(&v, addr, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && v != 0) e = cudaMemset(addr, 0, sizeof(int));
+    if (e != cudaSuccess) {
+        set_cuda_error(e, "flashmhf_device_status");
+        return FLASHMHF_ERR_CUDA;
+    }
+    if (code) *code = v;
+    return v == 0 ? FLASHMHF_OK : FLASHMHF_ERR_DEVICE_TIMEOUT;
+}
+
+}  // extern "C"

@@ -1,0 +1,30 @@
+// Internal launch interface between the C-ABI layer (api.cu) and the kernel translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/flashmhf.h"
+
+namespace fmhf {
+
+// Device status word: 0, or the code of the first bounded wait that ran out.
+int *device_status_ptr();  // device address of the per-device status word (resolved once per device)
+
+// ---- fp32 check kernels (CUDA cores) -------------------------------------------------------
+cudaError_t simt_forward(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch);
+cudaError_t simt_backward(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch);
+
+// ---- bf16 tensor-core kernels (tcgen05 / TMEM / TMA) ---------------------------------------
+// Each returns a flashmhf_status (tensor-map encoding can fail with BAD_STRIDE / CUDA).
+int tc_forward(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch);
+int tc_backward(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch);
+size_t tc_backward_workspace_bytes(const flashmhf_dims &d);
+
+void set_cuda_error(cudaError_t e, const char *where);
+
+// Kernel-boundary marks for the profiling aid (flashmhf_profile_begin/end): records an event on
+// `st` tagged `tag` when profiling is on, does nothing otherwise.
+enum { kMarkStart = 0, kMarkFwd = 1, kMarkBwdDq = 2, kMarkBwdDw = 3, kMarkBwdReduce = 4 };
+void prof_mark(cudaStream_t st, int tag);
+
+}  // namespace fmhf

@@ -1,0 +1,715 @@
+// Backward kernels, bf16, sm_100a.  The [T, E*d_e] intermediate is recomputed block by block.
+//
+//   M = Q K^T, N = Q U^T, sg = sigmoid(M), s = M*sg, dA = dO V^T          (per 64-row weight block)
+//   dR_e = rowsum(dA*s*N), dM = dA*(r*N)*(sg + s*(1-sg)), dN = dA*s*r, A = s*N*r
+//   dQ += dM K + dN U ;  dK = sum_t dM^T Q ;  dU = sum_t dN^T Q ;  dV = sum_t A^T dO
+//
+// Two kernels, each the sole owner of its accumulators (no floating-point atomics, bit-reproducible):
+//
+// bwd_dq_kernel  -- token-stationary.  One CTA owns 128 token rows of one (batch, head): Q and dO
+//   tiles stay in shared memory, the head's weights stream through (K/U ring of 3, V ring of 2).
+//   Tensor memory: dQ accumulator + two buffers of {S = [M|N] (128 cols), dA (64 cols)}.
+//   Produces dQ (TMA store) and dR (direct stores).
+//
+// bwd_dw_kernel  -- weight-stationary.  One CTA owns one 64-row block of K, U and V of one K/U/V
+//   head and a contiguous range of token tiles (the token axis is split `nsplit` ways to fill the
+//   machine).  Weights stay in shared memory, {Q, dO} tiles stream through a ring of 2.
+//   Tensor memory: [dK;dU] accumulator (128 lanes), dV accumulator (M = 64), S, dA.
+//   Each CTA writes fp32 partial sums to the workspace; dw_reduce_kernel adds the splits in a fixed
+//   order and writes bf16 dK, dU, dV.
+//
+// Both use 384 threads: warp 0 TMA producer, warp 1 MMA issuer and tensor-memory owner, warps 4-11
+// element-wise math (warp % 4 = TMEM lane quarter, (warp-4)/4 = which 32 of the 64 block columns).
+#include "kernels.h"
+#include "tc_common.cuh"
+#include "tensormap.cuh"
+
+namespace fmhf {
+namespace {
+
+constexpr int kBT = 128, kBI = 64, kThreads = 384, kActThreads = 256;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTile = kBT * 128;    // one 128-row x 64-col SW128 chunk: 16 KB
+constexpr uint32_t kWChunk = kBI * 128;  // one 64-row x 64-col chunk: 8 KB
+constexpr int kNumSMs = 148;
+
+// Element-wise backward math for one (token, intermediate column) pair.
+struct BwdElem {
+    float dm, dn, a, dr;
+};
+__device__ __forceinline__ BwdElem bwd_elem(float m, float n, float da, float r) {
+    const float sg = fast_sigmoid(m);
+    const float s = m * sg;
+    const float sn = s * n;
+    const float t = da * r;
+    BwdElem o;
+    o.dr = da * sn;
+    o.a = sn * r;
+    o.dn = t * s;
+    o.dm = t * n * (fmaf(-s, sg, s) + sg);  // silu'(m) = sg + s*(1-sg)
+    return o;
+}
+
+// =============================================================================================
+//                                       dQ / dR kernel
+// =============================================================================================
+template <int DH>
+struct DqSmem {
+    static constexpr int kChunks = (DH + 63) / 64;
+    static constexpr uint32_t kQBytes = kChunks * kTile;
+    static constexpr uint32_t kKUStage = kChunks * 2 * kWChunk;  // per chunk: [K;U] = 128 rows
+    static constexpr uint32_t kVStage = kChunks * kWChunk;
+    static constexpr int kKUStages = 3, kVStages = 2;
+    static constexpr uint32_t kPBytes = 2 * kTile;  // [dM | dN]
+    static constexpr uint32_t kOffQ = 0;
+    static constexpr uint32_t kOffdO = kOffQ + kQBytes;
+    static constexpr uint32_t kOffKU = kOffdO + kQBytes;
+    static constexpr uint32_t kOffV = kOffKU + kKUStages * kKUStage;
+    static constexpr uint32_t kOffP = kOffV + kVStages * kVStage;
+    static constexpr uint32_t kOffCtl = kOffP + kPBytes;
+    static constexpr uint32_t kCtlBytes = 256 + 2 * 128 * 4;  // barriers + two dR exchange rows
+    static constexpr uint32_t kTotal = kOffCtl + kCtlBytes + 1024;
+};
+
+enum { DQ_QFULL = 0, DQ_KUFULL = 1, DQ_KUEMPTY = 4, DQ_VFULL = 7, DQ_VEMPTY = 9, DQ_SFULL = 11, DQ_SEMPTY = 13,
+       DQ_PFULL = 15, DQ_PEMPTY = 16, DQ_ACCFULL = 17, DQ_DRFULL = 18, DQ_BARS = 20 };
+
+struct DqArgs {
+    const float *R;
+    long long r_sb, r_sh, r_ss;
+    float *dR;
+    long long dr_sb, dr_sh, dr_ss;
+    int S, E, De, G;
+    int *status;
+};
+
+template <int DH>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+              const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmU,
+              const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdQ, const DqArgs args) {
+    using L = DqSmem<DH>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *gbase = smem_raw + (base - raw);
+    const uint32_t sQ = base + L::kOffQ, sdO = base + L::kOffdO, sKU = base + L::kOffKU, sV = base + L::kOffV,
+                   sP = base + L::kOffP, sBar = base + L::kOffCtl;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gbase + L::kOffCtl + DQ_BARS * 8);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gbase + L::kOffCtl + DQ_BARS * 8 + 4);
+    volatile float *drx = reinterpret_cast<volatile float *>(gbase + L::kOffCtl + 256);  // [2][128]
+    auto bar = [&](int i) { return sBar + 8u * i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * kBT, h = blockIdx.y, b = blockIdx.z, hk = h / args.G;
+    const int bpe = args.De / kBI, nblk = args.E * bpe;
+    const WaitCtl ctl{abort_flag, args.status};
+    constexpr int W = kKernelBwdDq * 100;
+    constexpr uint32_t kColAcc = 0, kColS0 = 128, kBufStride = 192, kColdA = 128;  // dA offset inside a buffer
+
+    if (threadIdx.x == 0) {
+        *abort_flag = (*reinterpret_cast<volatile int *>(args.status) != 0);  // an earlier CTA gave up: drain fast
+        mbar_init(bar(DQ_QFULL), 1);
+        for (int s = 0; s < L::kKUStages; ++s) { mbar_init(bar(DQ_KUFULL + s), 1); mbar_init(bar(DQ_KUEMPTY + s), 1); }
+        for (int s = 0; s < L::kVStages; ++s) { mbar_init(bar(DQ_VFULL + s), 1); mbar_init(bar(DQ_VEMPTY + s), 1); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(DQ_SFULL + i), 1);
+            mbar_init(bar(DQ_SEMPTY + i), kActThreads);
+            mbar_init(bar(DQ_DRFULL + i), kActThreads / 2);
+        }
+        mbar_init(bar(DQ_PFULL), kActThreads);
+        mbar_init(bar(DQ_PEMPTY), 1);
+        mbar_init(bar(DQ_ACCFULL), 1);
+        fence_mbar_init();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const bool dead = *abort_flag != 0;
+
+    if (dead) {
+        // nothing: fall through to the teardown
+    } else if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmdO); tma_prefetch_desc(&tmK);
+            tma_prefetch_desc(&tmU); tma_prefetch_desc(&tmV);
+            mbar_arrive_expect_tx(bar(DQ_QFULL), 2 * L::kQBytes);
+            for (int c = 0; c < L::kChunks; ++c) {
+                tma_load_4d(sQ + c * kTile, &tmQ, bar(DQ_QFULL), c * 64, t0, h, b);
+                tma_load_4d(sdO + c * kTile, &tmdO, bar(DQ_QFULL), c * 64, t0, h, b);
+            }
+            for (int j = 0; j < nblk; ++j) {
+                const int sk = j % L::kKUStages, nk = j / L::kKUStages, sv = j % L::kVStages, nv = j / L::kVStages;
+                const int row = j * kBI;
+                if (!mbar_wait(bar(DQ_KUEMPTY + sk), (nk & 1) ^ 1, ctl, W + 1)) break;
+                mbar_arrive_expect_tx(bar(DQ_KUFULL + sk), L::kKUStage);
+                for (int c = 0; c < L::kChunks; ++c) {
+                    const uint32_t d = sKU + sk * L::kKUStage + c * 2 * kWChunk;
+                    tma_load_3d(d, &tmK, bar(DQ_KUFULL + sk), c * 64, row, hk);
+                    tma_load_3d(d + kWChunk, &tmU, bar(DQ_KUFULL + sk), c * 64, row, hk);
+                }
+                if (!mbar_wait(bar(DQ_VEMPTY + sv), (nv & 1) ^ 1, ctl, W + 2)) break;
+                mbar_arrive_expect_tx(bar(DQ_VFULL + sv), L::kVStage);
+                for (int c = 0; c < L::kChunks; ++c)
+                    tma_load_3d(sV + sv * L::kVStage + c * kWChunk, &tmV, bar(DQ_VFULL + sv), c * 64, row, hk);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idS = umma_idesc(128, 2 * kBI, false, false);  // S  = Q  [K;U]^T
+            constexpr uint32_t idA = umma_idesc(128, kBI, false, false);      // dA = dO V^T
+            constexpr uint32_t idQ = umma_idesc(128, DH, false, true);        // dQ += [dM|dN] [K;U]
+            auto gemm3 = [&](int jj) -> bool {
+                const int sk = jj % L::kKUStages;
+                if (!mbar_wait(bar(DQ_PFULL), jj & 1, ctl, W + 6)) return false;
+                tc_fence_after();
+                const uint32_t ku = sKU + sk * L::kKUStage;
+#pragma unroll
+                for (int k = 0; k < 8; ++k)  // K = 128: 64 columns of dM (rows of K) then 64 of dN (rows of U)
+                    umma_ss(tmem + kColAcc, desc_kmajor(sP + (k >> 2) * kTile + (k & 3) * 32),
+                            desc_mnmajor(ku + k * 2048, 2 * kWChunk), idQ, (jj > 0 || k > 0) ? 1u : 0u);
+                umma_commit(bar(DQ_KUEMPTY + sk));
+                umma_commit(bar(DQ_PEMPTY));
+                return true;
+            };
+            bool ok = mbar_wait(bar(DQ_QFULL), 0, ctl, W + 3);
+            for (int j = 0; ok && j < nblk; ++j) {
+                const int sk = j % L::kKUStages, nk = j / L::kKUStages, sv = j % L::kVStages, nv = j / L::kVStages;
+                const int bb = j & 1, nb = j >> 1;
+                if (!mbar_wait(bar(DQ_KUFULL + sk), nk & 1, ctl, W + 4)) { ok = false; break; }
+                if (!mbar_wait(bar(DQ_VFULL + sv), nv & 1, ctl, W + 4)) { ok = false; break; }
+                if (!mbar_wait(bar(DQ_SEMPTY + bb), (nb & 1) ^ 1, ctl, W + 5)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t ku = sKU + sk * L::kKUStage, vv = sV + sv * L::kVStage;
+                const uint32_t tS = tmem + kColS0 + bb * kBufStride;
+#pragma unroll
+                for (int k = 0; k < DH / 16; ++k) {
+                    const int c = k >> 2, kk = k & 3;
+                    umma_ss(tS, desc_kmajor(sQ + c * kTile + kk * 32), desc_kmajor(ku + c * 2 * kWChunk + kk * 32), idS,
+                            k > 0 ? 1u : 0u);
+                }
+#pragma unroll
+                for (int k = 0; k < DH / 16; ++k) {
+                    const int c = k >> 2, kk = k & 3;
+                    umma_ss(tS + kColdA, desc_kmajor(sdO + c * kTile + kk * 32), desc_kmajor(vv + c * kWChunk + kk * 32),
+                            idA, k > 0 ? 1u : 0u);
+                }
+                umma_commit(bar(DQ_VEMPTY + sv));
+                umma_commit(bar(DQ_SFULL + bb));
+                if (j > 0) ok = gemm3(j - 1);
+            }
+            if (ok) ok = gemm3(nblk - 1);
+            umma_commit(bar(DQ_ACCFULL));
+        }
+    } else if (warp >= 4) {
+        const int quarter = warp & 3, half = (warp - 4) >> 2;
+        const int row = quarter * 32 + lane, t = t0 + row;
+        const bool in_range = t < args.S;
+        const float *rrow = args.R + (long long)b * args.r_sb + (long long)h * args.r_sh + (long long)t * args.r_ss;
+        float *drrow = args.dR + (long long)b * args.dr_sb + (long long)h * args.dr_sh + (long long)t * args.dr_ss;
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+        float r_cur = 0.f, r_next = in_range ? __ldg(rrow) : 0.f, dr_acc = 0.f;
+        bool ok = true;
+        for (int j = 0; j < nblk; ++j) {
+            const int bb = j & 1, nb = j >> 1, e = j / bpe;
+            if (j % bpe == 0) {
+                r_cur = r_next;
+                r_next = (in_range && e + 1 < args.E) ? __ldg(rrow + e + 1) : 0.f;
+                dr_acc = 0.f;
+            }
+            if (!mbar_wait(bar(DQ_SFULL + bb), nb & 1, ctl, W + 7)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t tS = lane_base + kColS0 + bb * kBufStride + half * 32;
+            uint32_t pm[16], pn[16];  // packed bf16 pairs of dM, dN for this thread's 32 columns
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub) {
+                uint32_t m[16], n[16], da[16];
+                tmem_ld16(tS + sub * 16, m);
+                tmem_ld16(tS + kBI + sub * 16, n);
+                tmem_ld16(tS + kColdA + sub * 16, da);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const BwdElem x0 = bwd_elem(__uint_as_float(m[2 * i]), __uint_as_float(n[2 * i]),
+                                                __uint_as_float(da[2 * i]), r_cur);
+                    const BwdElem x1 = bwd_elem(__uint_as_float(m[2 * i + 1]), __uint_as_float(n[2 * i + 1]),
+                                                __uint_as_float(da[2 * i + 1]), r_cur);
+                    dr_acc += x0.dr + x1.dr;
+                    pm[sub * 8 + i] = pack_bf16(x0.dm, x1.dm);
+                    pn[sub * 8 + i] = pack_bf16(x0.dn, x1.dn);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar(DQ_SEMPTY + bb));
+            if (!mbar_wait(bar(DQ_PEMPTY), (j & 1) ^ 1, ctl, W + 8)) { ok = false; break; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t off = sw128_offset(row, half * 4 + i);
+                st_shared_v4(sP + off, pm[4 * i], pm[4 * i + 1], pm[4 * i + 2], pm[4 * i + 3]);
+                st_shared_v4(sP + kTile + off, pn[4 * i], pn[4 * i + 1], pn[4 * i + 2], pn[4 * i + 3]);
+            }
+            fence_async_smem();
+            mbar_arrive(bar(DQ_PFULL));
+            if ((j + 1) % bpe == 0) {  // sub-network finished: add the two column halves of dR_e
+                const int xb = e & 1;
+                if (half == 1) {
+                    drx[xb * 128 + row] = dr_acc;
+                    mbar_arrive(bar(DQ_DRFULL + xb));
+                } else {
+                    if (!mbar_wait(bar(DQ_DRFULL + xb), (e >> 1) & 1, ctl, W + 9)) { ok = false; break; }
+                    if (in_range) drrow[e] = dr_acc + drx[xb * 128 + row];
+                }
+            }
+        }
+        if (ok) ok = mbar_wait(bar(DQ_ACCFULL), 0, ctl, W + 10);
+        if (ok) {
+            tc_fence_after();
+            constexpr int kColsPerHalf = DH / 2;
+            const int c0 = half * kColsPerHalf;
+#pragma unroll
+            for (int g = 0; g < kColsPerHalf / 16; ++g) {
+                uint32_t o[16];
+                tmem_ld16(lane_base + kColAcc + c0 + g * 16, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int v = 0; v < 2; ++v) {
+                    const int col = c0 + g * 16 + v * 8;
+                    const uint32_t dst = sQ + (col >> 6) * kTile + sw128_offset(row, (col & 63) >> 3);
+                    st_shared_v4(dst, pack_bf16(__uint_as_float(o[8 * v + 0]), __uint_as_float(o[8 * v + 1])),
+                                 pack_bf16(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3])),
+                                 pack_bf16(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5])),
+                                 pack_bf16(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7])));
+                }
+            }
+            tc_fence_before();
+            fence_async_smem();
+        }
+        named_bar_sync(1, kActThreads);
+        if (ok && warp == 4 && lane == 0 && !*abort_flag) {
+            for (int c = 0; c < L::kChunks; ++c) tma_store_4d(&tmdQ, sQ + c * kTile, c * 64, t0, h, b);
+            tma_store_commit();
+            tma_store_wait_all();
+        }
+    }
+
+    __syncwarp();
+    if (*abort_flag) {
+        const long long t_end = clock64() + (1LL << 19);
+        while (clock64() < t_end) __nanosleep(256);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// =============================================================================================
+//                                    dK / dU / dV kernel
+// =============================================================================================
+template <int DH>
+struct DwSmem {
+    static constexpr int kChunks = (DH + 63) / 64;
+    static constexpr uint32_t kWBytes = 3 * kChunks * kWChunk;  // [K;U] chunks then V chunks
+    static constexpr uint32_t kOffWV = 2 * kChunks * kWChunk;
+    static constexpr uint32_t kTokStage = 2 * kChunks * kTile;  // Q chunks then dO chunks
+    static constexpr int kTokStages = 2;
+    static constexpr uint32_t kOffW = 0;
+    static constexpr uint32_t kOffTok = kOffW + kWBytes;
+    static constexpr uint32_t kOffP = kOffTok + kTokStages * kTokStage;  // [dM | dN] : 2 x 16 KB
+    static constexpr uint32_t kOffA = kOffP + 2 * kTile;                 // A : 16 KB
+    static constexpr uint32_t kOffCtl = kOffA + kTile;
+    static constexpr uint32_t kTotal = kOffCtl + 256 + 1024;
+};
+
+enum { DW_WFULL = 0, DW_TFULL = 1, DW_TEMPTY = 3, DW_SFULL = 5, DW_SEMPTY = 6, DW_PFULL = 7, DW_PEMPTY = 8,
+       DW_ACCFULL = 9, DW_BARS = 10 };
+
+struct DwArgs {
+    const float *R;
+    long long r_sb, r_sh, r_ss;
+    float *ws;  // [nsplit][3][Hkuv][I][DH] fp32 partial sums
+    int S, E, De, G, B, Hkuv;
+    int tiles_per_seq, tiles_total, tiles_per_split;
+    int *status;
+};
+
+template <int DH>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+              const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmU,
+              const __grid_constant__ CUtensorMap tmV, const DwArgs args) {
+    using L = DwSmem<DH>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *gbase = smem_raw + (base - raw);
+    const uint32_t sW = base + L::kOffW, sTok = base + L::kOffTok, sP = base + L::kOffP, sA = base + L::kOffA,
+                   sBar = base + L::kOffCtl;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gbase + L::kOffCtl + DW_BARS * 8);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gbase + L::kOffCtl + DW_BARS * 8 + 4);
+    auto bar = [&](int i) { return sBar + 8u * i; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int jblk = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
+    const int e = (jblk * kBI) / args.De;
+    const int tile_begin = split * args.tiles_per_split;
+    const int tile_end = min(tile_begin + args.tiles_per_split, args.tiles_total);
+    const int ntiles = tile_end - tile_begin;  // >= 1 by construction of the grid
+    const WaitCtl ctl{abort_flag, args.status};
+    constexpr int W = kKernelBwdDw * 100;
+    constexpr uint32_t kColKU = 0, kColV = 128, kColS = 256, kColdA = 384;
+
+    auto tile_coords = [&](int i, int &ts, int &hh, int &bb) {  // token tile i of this CTA -> (seq tile, head, batch)
+        const int ti = tile_begin + i;
+        ts = ti % args.tiles_per_seq;
+        const int rest = ti / args.tiles_per_seq;
+        hh = hk * args.G + rest % args.G;
+        bb = rest / args.G;
+    };
+
+    if (threadIdx.x == 0) {
+        *abort_flag = (*reinterpret_cast<volatile int *>(args.status) != 0);  // an earlier CTA gave up: drain fast
+        mbar_init(bar(DW_WFULL), 1);
+        for (int s = 0; s < L::kTokStages; ++s) { mbar_init(bar(DW_TFULL + s), 1); mbar_init(bar(DW_TEMPTY + s), 1); }
+        mbar_init(bar(DW_SFULL), 1);
+        mbar_init(bar(DW_SEMPTY), kActThreads);
+        mbar_init(bar(DW_PFULL), kActThreads);
+        mbar_init(bar(DW_PEMPTY), 1);
+        mbar_init(bar(DW_ACCFULL), 1);
+        fence_mbar_init();
+    }
+    if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const bool dead = *abort_flag != 0;
+
+    if (dead) {
+        // nothing: fall through to the teardown
+    } else if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmdO); tma_prefetch_desc(&tmK);
+            tma_prefetch_desc(&tmU); tma_prefetch_desc(&tmV);
+            mbar_arrive_expect_tx(bar(DW_WFULL), L::kWBytes);
+            const int row = jblk * kBI;
+            for (int c = 0; c < L::kChunks; ++c) {
+                tma_load_3d(sW + c * 2 * kWChunk, &tmK, bar(DW_WFULL), c * 64, row, hk);
+                tma_load_3d(sW + c * 2 * kWChunk + kWChunk, &tmU, bar(DW_WFULL), c * 64, row, hk);
+                tma_load_3d(sW + L::kOffWV + c * kWChunk, &tmV, bar(DW_WFULL), c * 64, row, hk);
+            }
+            for (int i = 0; i < ntiles; ++i) {
+                const int s = i % L::kTokStages, n = i / L::kTokStages;
+                int ts, hh, bb;
+                tile_coords(i, ts, hh, bb);
+                if (!mbar_wait(bar(DW_TEMPTY + s), (n & 1) ^ 1, ctl, W + 1)) break;
+                mbar_arrive_expect_tx(bar(DW_TFULL + s), L::kTokStage);
+                const uint32_t d = sTok + s * L::kTokStage;
+                for (int c = 0; c < L::kChunks; ++c) {
+                    tma_load_4d(d + c * kTile, &tmQ, bar(DW_TFULL + s), c * 64, ts * kBT, hh, bb);
+                    tma_load_4d(d + (L::kChunks + c) * kTile, &tmdO, bar(DW_TFULL + s), c * 64, ts * kBT, hh, bb);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idS = umma_idesc(128, 2 * kBI, false, false);  // S  = Q  [K;U]^T
+            constexpr uint32_t idA = umma_idesc(128, kBI, false, false);      // dA = dO V^T
+            constexpr uint32_t idKU = umma_idesc(128, DH, true, true);        // [dK;dU] += [dM|dN]^T Q
+            constexpr uint32_t idV = umma_idesc(64, DH, true, true);          // dV      += A^T dO
+            auto gemm34 = [&](int ii) -> bool {
+                const int s = ii % L::kTokStages;
+                if (!mbar_wait(bar(DW_PFULL), ii & 1, ctl, W + 6)) return false;
+                tc_fence_after();
+                const uint32_t q0 = sTok + s * L::kTokStage, g0 = q0 + L::kChunks * kTile;
+#pragma unroll
+                for (int k = 0; k < kBT / 16; ++k)
+                    umma_ss(tmem + kColKU, desc_mnmajor(sP + k * 2048, kTile), desc_mnmajor(q0 + k * 2048, kTile), idKU,
+                            (ii > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < kBT / 16; ++k)
+                    umma_ss(tmem + kColV, desc_mnmajor(sA + k * 2048, kTile), desc_mnmajor(g0 + k * 2048, kTile), idV,
+                            (ii > 0 || k > 0) ? 1u : 0u);
+                umma_commit(bar(DW_TEMPTY + s));
+                umma_commit(bar(DW_PEMPTY));
+                return true;
+            };
+            bool ok = mbar_wait(bar(DW_WFULL), 0, ctl, W + 3);
+            for (int i = 0; ok && i < ntiles; ++i) {
+                const int s = i % L::kTokStages, n = i / L::kTokStages;
+                if (!mbar_wait(bar(DW_TFULL + s), n & 1, ctl, W + 4)) { ok = false; break; }
+                if (!mbar_wait(bar(DW_SEMPTY), (i & 1) ^ 1, ctl, W + 5)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t q0 = sTok + s * L::kTokStage, g0 = q0 + L::kChunks * kTile;
+#pragma unroll
+                for (int k = 0; k < DH / 16; ++k) {
+                    const int c = k >> 2, kk = k & 3;
+                    umma_ss(tmem + kColS, desc_kmajor(q0 + c * kTile + kk * 32),
+                            desc_kmajor(sW + c * 2 * kWChunk + kk * 32), idS, k > 0 ? 1u : 0u);
+                }
+#pragma unroll
+                for (int k = 0; k < DH / 16; ++k) {
+                    const int c = k >> 2, kk = k & 3;
+                    umma_ss(tmem + kColdA, desc_kmajor(g0 + c * kTile + kk * 32),
+                            desc_kmajor(sW + L::kOffWV + c * kWChunk + kk * 32), idA, k > 0 ? 1u : 0u);
+                }
+                umma_commit(bar(DW_SFULL));
+                if (i > 0) ok = gemm34(i - 1);
+            }
+            if (ok) ok = gemm34(ntiles - 1);
+            umma_commit(bar(DW_ACCFULL));
+        }
+    } else if (warp >= 4) {
+        const int quarter = warp & 3, half = (warp - 4) >> 2;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+        bool ok = true;
+        float r_next;
+        {
+            int ts, hh, bb;
+            tile_coords(0, ts, hh, bb);
+            const int t = ts * kBT + row;
+            r_next = (t < args.S) ? __ldg(args.R + (long long)bb * args.r_sb + (long long)hh * args.r_sh +
+                                          (long long)t * args.r_ss + e) : 0.f;
+        }
+        for (int i = 0; i < ntiles; ++i) {
+            const float r = r_next;
+            if (i + 1 < ntiles) {
+                int ts, hh, bb;
+                tile_coords(i + 1, ts, hh, bb);
+                const int t = ts * kBT + row;
+                r_next = (t < args.S) ? __ldg(args.R + (long long)bb * args.r_sb + (long long)hh * args.r_sh +
+                                              (long long)t * args.r_ss + e) : 0.f;
+            }
+            if (!mbar_wait(bar(DW_SFULL), i & 1, ctl, W + 7)) { ok = false; break; }
+            tc_fence_after();
+            uint32_t pm[16], pn[16], pa[16];
+#pragma unroll
+            for (int sub = 0; sub < 2; ++sub) {
+                uint32_t m[16], n[16], da[16];
+                const uint32_t c = half * 32 + sub * 16;
+                tmem_ld16(lane_base + kColS + c, m);
+                tmem_ld16(lane_base + kColS + kBI + c, n);
+                tmem_ld16(lane_base + kColdA + c, da);
+                tmem_ld_wait();
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const BwdElem x0 = bwd_elem(__uint_as_float(m[2 * q]), __uint_as_float(n[2 * q]),
+                                                __uint_as_float(da[2 * q]), r);
+                    const BwdElem x1 = bwd_elem(__uint_as_float(m[2 * q + 1]), __uint_as_float(n[2 * q + 1]),
+                                                __uint_as_float(da[2 * q + 1]), r);
+                    pm[sub * 8 + q] = pack_bf16(x0.dm, x1.dm);
+                    pn[sub * 8 + q] = pack_bf16(x0.dn, x1.dn);
+                    pa[sub * 8 + q] = pack_bf16(x0.a, x1.a);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(bar(DW_SEMPTY));
+            if (!mbar_wait(bar(DW_PEMPTY), (i & 1) ^ 1, ctl, W + 8)) { ok = false; break; }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t off = sw128_offset(row, half * 4 + q);
+                st_shared_v4(sP + off, pm[4 * q], pm[4 * q + 1], pm[4 * q + 2], pm[4 * q + 3]);
+                st_shared_v4(sP + kTile + off, pn[4 * q], pn[4 * q + 1], pn[4 * q + 2], pn[4 * q + 3]);
+                st_shared_v4(sA + off, pa[4 * q], pa[4 * q + 1], pa[4 * q + 2], pa[4 * q + 3]);
+            }
+            fence_async_smem();
+            mbar_arrive(bar(DW_PFULL));
+        }
+        if (ok) ok = mbar_wait(bar(DW_ACCFULL), 0, ctl, W + 9);
+        if (ok) {
+            tc_fence_after();
+            // fp32 partial sums -> workspace[split][which][hk][row][DH]
+            const long long I = (long long)args.E * args.De;
+            const long long plane = (long long)args.Hkuv * I * DH;
+            float *wsb = args.ws + (long long)split * 3 * plane + ((long long)hk * I + (long long)jblk * kBI) * DH;
+            constexpr int kColsPerHalf = DH / 2;
+            const int c0 = half * kColsPerHalf;
+            {   // [dK;dU]: lane = row of the stacked block (0-63 dK, 64-127 dU)
+                float *dst = wsb + (row < kBI ? 0 : plane) + (long long)(row & (kBI - 1)) * DH + c0;
+#pragma unroll
+                for (int g = 0; g < kColsPerHalf / 16; ++g) {
+                    uint32_t o[16];
+                    tmem_ld16(lane_base + kColKU + c0 + g * 16, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int v = 0; v < 4; ++v)
+                        *reinterpret_cast<float4 *>(dst + g * 16 + v * 4) =
+                            make_float4(__uint_as_float(o[4 * v]), __uint_as_float(o[4 * v + 1]),
+                                        __uint_as_float(o[4 * v + 2]), __uint_as_float(o[4 * v + 3]));
+                }
+            }
+            {   // dV (M = 64 accumulator): row r lives in TMEM lane 32*(r/16) + r%16
+                float *dst = wsb + 2 * plane + (long long)(quarter * 16 + (lane & 15)) * DH + c0;
+#pragma unroll
+                for (int g = 0; g < kColsPerHalf / 16; ++g) {
+                    uint32_t o[16];
+                    tmem_ld16(lane_base + kColV + c0 + g * 16, o);
+                    tmem_ld_wait();
+                    if (lane < 16) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            *reinterpret_cast<float4 *>(dst + g * 16 + v * 4) =
+                                make_float4(__uint_as_float(o[4 * v]), __uint_as_float(o[4 * v + 1]),
+                                            __uint_as_float(o[4 * v + 2]), __uint_as_float(o[4 * v + 3]));
+                    }
+                }
+            }
+            tc_fence_before();
+        }
+    }
+
+    __syncwarp();
+    if (*abort_flag) {
+        const long long t_end = clock64() + (1LL << 19);
+        while (clock64() < t_end) __nanosleep(256);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+// Sum the token-axis splits in index order and write bf16 gradients (4 elements per thread).
+struct ReduceArgs {
+    const float *ws;
+    __nv_bfloat16 *out[3];
+    long long s_head[3], s_row[3];
+    long long plane;  // Hkuv * I * DH
+    int nsplit, I, DH;
+};
+__global__ void __launch_bounds__(256) dw_reduce_kernel(const ReduceArgs a) {
+    const long long n4 = 3 * a.plane / 4;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n4;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long el = idx * 4;
+        float4 acc = *reinterpret_cast<const float4 *>(a.ws + el);
+        for (int s = 1; s < a.nsplit; ++s) {
+            const float4 v = *reinterpret_cast<const float4 *>(a.ws + (long long)s * 3 * a.plane + el);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const int which = (int)(el / a.plane);
+        const long long rem = el - (long long)which * a.plane;
+        const int c = (int)(rem % a.DH);
+        const long long rowi = rem / a.DH;
+        const int r = (int)(rowi % a.I), hk = (int)(rowi / a.I);
+        __nv_bfloat16 *o = a.out[which] + hk * a.s_head[which] + r * a.s_row[which] + c;
+        uint2 packed = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+        *reinterpret_cast<uint2 *>(o) = packed;
+    }
+}
+
+int choose_nsplit(long long items, int tiles_total) {
+    int best = 1;
+    double best_eff = 0.0;
+    for (int ns = 1; ns <= 16 && ns <= tiles_total; ++ns) {
+        const long long ctas = items * ns;
+        const long long waves = (ctas + kNumSMs - 1) / kNumSMs;
+        const double eff = (double)ctas / (double)(waves * kNumSMs);
+        if (eff > best_eff + 1e-9) { best_eff = eff; best = ns; }
+        if (eff >= 0.9) return ns;
+    }
+    return best;
+}
+
+struct DwPlan {
+    int tiles_per_seq, tiles_total, nsplit, tiles_per_split;
+};
+DwPlan dw_plan(const flashmhf_dims &d) {
+    DwPlan p;
+    const int G = d.H / d.Hkuv;
+    p.tiles_per_seq = (d.S + kBT - 1) / kBT;
+    p.tiles_total = p.tiles_per_seq * G * d.B;
+    const long long items = (long long)d.Hkuv * ((long long)d.E * d.De / kBI);
+    const int ns = choose_nsplit(items, p.tiles_total);
+    p.tiles_per_split = (p.tiles_total + ns - 1) / ns;
+    p.nsplit = (p.tiles_total + p.tiles_per_split - 1) / p.tiles_per_split;  // no empty split
+    return p;
+}
+
+template <int DH>
+int launch_bwd(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch) {
+    const flashmhf_dims &d = p.d;
+    CUtensorMap tmQ, tmdO, tmK, tmU, tmV, tmdQ;
+    int rc;
+    if ((rc = encode_act_map(&tmQ, p.Q, d, kBT)) != 0) return rc;
+    if ((rc = encode_act_map(&tmdO, p.dO, d, kBT)) != 0) return rc;
+    if ((rc = encode_weight_map(&tmK, p.K, d, kBI)) != 0) return rc;
+    if ((rc = encode_weight_map(&tmU, p.U, d, kBI)) != 0) return rc;
+    if ((rc = encode_weight_map(&tmV, p.V, d, kBI)) != 0) return rc;
+    if ((rc = encode_act_map(&tmdQ, p.dQ, d, kBT)) != 0) return rc;
+    for (const flashmhf_tensor *t : {&p.dK, &p.dU, &p.dV}) {
+        if (d.E > 1 && t->stride[1] != (int64_t)d.De * t->stride[2]) return FLASHMHF_ERR_BAD_STRIDE;
+        if (t->stride[2] % 4 != 0 || t->stride[0] % 4 != 0) return FLASHMHF_ERR_BAD_STRIDE;
+    }
+    cudaError_t e;
+    e = cudaFuncSetAttribute(bwd_dq_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DqSmem<DH>::kTotal);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(bwd_dw_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DwSmem<DH>::kTotal);
+    if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(bwd kernels)"); return FLASHMHF_ERR_CUDA; }
+
+    const int G = d.H / d.Hkuv;
+    DqArgs qa{static_cast<const float *>(p.R.ptr), p.R.stride[0], p.R.stride[1], p.R.stride[2],
+              static_cast<float *>(p.dR.ptr), p.dR.stride[0], p.dR.stride[1], p.dR.stride[2],
+              d.S, d.E, d.De, G, device_status_ptr()};
+    dim3 gq((d.S + kBT - 1) / kBT, d.H, d.B);
+    prof_mark(st, kMarkStart);
+    bwd_dq_kernel<DH><<<gq, kThreads, DqSmem<DH>::kTotal, st>>>(tmQ, tmdO, tmK, tmU, tmV, tmdQ, qa);
+    prof_mark(st, kMarkBwdDq);
+    *n_launch += 1;
+    if ((e = cudaGetLastError()) != cudaSuccess) { set_cuda_error(e, "bwd_dq_kernel launch"); return FLASHMHF_ERR_CUDA; }
+
+    const DwPlan pl = dw_plan(d);
+    DwArgs wa{static_cast<const float *>(p.R.ptr), p.R.stride[0], p.R.stride[1], p.R.stride[2],
+              static_cast<float *>(p.workspace), d.S, d.E, d.De, G, d.B, d.Hkuv,
+              pl.tiles_per_seq, pl.tiles_total, pl.tiles_per_split, device_status_ptr()};
+    dim3 gw(d.E * d.De / kBI, d.Hkuv, pl.nsplit);
+    bwd_dw_kernel<DH><<<gw, kThreads, DwSmem<DH>::kTotal, st>>>(tmQ, tmdO, tmK, tmU, tmV, wa);
+    prof_mark(st, kMarkBwdDw);
+    *n_launch += 1;
+    if ((e = cudaGetLastError()) != cudaSuccess) { set_cuda_error(e, "bwd_dw_kernel launch"); return FLASHMHF_ERR_CUDA; }
+
+    ReduceArgs ra;
+    ra.ws = static_cast<const float *>(p.workspace);
+    const flashmhf_tensor *outs[3] = {&p.dK, &p.dU, &p.dV};
+    for (int i = 0; i < 3; ++i) {
+        ra.out[i] = static_cast<__nv_bfloat16 *>(outs[i]->ptr);
+        ra.s_head[i] = outs[i]->stride[0];
+        ra.s_row[i] = outs[i]->stride[2];
+    }
+    ra.I = d.E * d.De;
+    ra.DH = DH;
+    ra.plane = (long long)d.Hkuv * ra.I * DH;
+    ra.nsplit = pl.nsplit;
+    const long long n4 = 3 * ra.plane / 4;
+    const int blocks = (int)((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
+    dw_reduce_kernel<<<blocks, 256, 0, st>>>(ra);
+    prof_mark(st, kMarkBwdReduce);
+    *n_launch += 1;
+    if ((e = cudaGetLastError()) != cudaSuccess) { set_cuda_error(e, "dw_reduce_kernel launch"); return FLASHMHF_ERR_CUDA; }
+    return FLASHMHF_OK;
+}
+
+}  // namespace
+
+size_t tc_backward_workspace_bytes(const flashmhf_dims &d) {
+    const DwPlan pl = dw_plan(d);
+    return (size_t)pl.nsplit * 3 * (size_t)d.Hkuv * (size_t)d.E * d.De * d.Dh * sizeof(float);
+}
+
+int tc_backward(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch) {
+    switch (p.d.Dh) {
+        case 64: return launch_bwd<64>(p, st, n_launch);
+        case 96: return launch_bwd<96>(p, st, n_launch);
+        case 128: return launch_bwd<128>(p, st, n_launch);
+        default: return FLASHMHF_ERR_BAD_SHAPE;
+    }
+}
+
+}  // namespace fmhf

@@ -1,0 +1,124 @@
+"""Host side of the operator: torch tensors in, C-ABI calls out.
+
+``flash_mhf(Q, K, U, V, R)`` has the call signature of the reference's
+``FlashMLPFunction.apply`` (kernels/triton/flash_mlp_moe.py:739-868) and of its ThunderKittens
+twin (kernels/thunderkittens/flash_ffn_moe_torch.py:5-24): it saves the five inputs, keeps no
+intermediate, and recomputes in backward.  PyTorch supplies device memory and the current stream;
+all arithmetic runs in the CUDA library."""
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+_DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32_CHECK}
+
+
+def _tensor(t):
+    return _lib.Tensor(t.data_ptr(), (C.c_int64 * 3)(*t.stride()[:3]))
+
+
+def _strided_ok(t, is_weight, de):
+    """Can the library address this tensor in place? (unit inner stride, 16-byte aligned outer strides, E/d_e collapse)"""
+    if t.stride(-1) != 1 and t.size(-1) != 1:
+        return False
+    if t.data_ptr() % 16:
+        return False
+    if t.dtype == torch.bfloat16:
+        for i in range(3):
+            if t.size(i) > 1 and (t.stride(i) % 8 or t.stride(i) <= 0):
+                return False
+    if is_weight and t.size(1) > 1 and t.stride(1) != de * t.stride(2):
+        return False
+    return True
+
+
+def _prep(t, is_weight=False, de=0):
+    return t if _strided_ok(t, is_weight, de) else t.contiguous()
+
+
+def _validate(Q, K, U, V, R):
+    if Q.dim() != 4 or K.dim() != 4 or R.dim() != 4:
+        raise ValueError("expected Q [B,H,S,d_h], K/U/V [H_kuv,E,d_e,d_h], R [B,H,S,E]")
+    B, H, S, dh = Q.shape
+    hk, E, de, dh2 = K.shape
+    if de % 64 != 0:
+        raise ValueError(f"Expert dimension {de} must be divisible by 64")
+    if U.shape != K.shape or V.shape != K.shape or dh2 != dh:
+        raise ValueError(f"K/U/V shapes must agree and end in d_h={dh}: {tuple(K.shape)}, {tuple(U.shape)}, {tuple(V.shape)}")
+    if hk < 1 or H % hk != 0:
+        raise ValueError(f"num_heads {H} must be a multiple of num_kuv_heads {hk}")
+    if tuple(R.shape) != (B, H, S, E):
+        raise ValueError(f"R must be {(B, H, S, E)}, got {tuple(R.shape)}")
+    if dh not in (64, 96, 128):
+        raise ValueError(f"head_dim {dh} not supported (64, 96 or 128)")
+    if Q.dtype not in _DT or any(t.dtype != Q.dtype for t in (K, U, V)):
+        raise TypeError("flash_mhf expects Q, K, U, V all in torch.bfloat16 (or all float32 for the check mode), got"
+                        f" Q={Q.dtype}, K={K.dtype}, V={V.dtype}, U={U.dtype}")
+    if not Q.is_cuda or any(t.device != Q.device for t in (K, U, V, R)):
+        raise ValueError("flash_mhf runs on CUDA tensors of one device; there is no CPU path")
+    return B, H, S, dh, hk, E, de
+
+
+def _dims(B, H, S, dh, hk, E, de, dtype):
+    return _lib.Dims(B, H, S, dh, hk, E, de, _DT[dtype])
+
+
+def forward_raw(Q, K, U, V, R, out=None):
+    """O = flashmhf_forward(...) on the current stream; no autograd."""
+    B, H, S, dh, hk, E, de = _validate(Q, K, U, V, R)
+    lib = _lib.load()
+    Q, K, U, V = _prep(Q), _prep(K, True, de), _prep(U, True, de), _prep(V, True, de)
+    R = R.to(torch.float32)
+    if R.stride(-1) != 1:
+        R = R.contiguous()
+    O = torch.empty_like(Q, memory_format=torch.contiguous_format) if out is None else out
+    p = _lib.FwdParams(_dims(B, H, S, dh, hk, E, de, Q.dtype), _tensor(Q), _tensor(K), _tensor(U), _tensor(V),
+                       _tensor(R), _tensor(O))
+    with torch.cuda.device(Q.device):
+        _lib.check(lib.flashmhf_forward(C.byref(p), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return O
+
+
+def backward_raw(Q, K, U, V, R, dO):
+    """(dQ, dK, dU, dV, dR) = flashmhf_backward(...) on the current stream; no autograd."""
+    B, H, S, dh, hk, E, de = _validate(Q, K, U, V, R)
+    if dO.shape != Q.shape:
+        raise AssertionError("grad_output shape should be the same as Q")
+    lib = _lib.load()
+    Q, K, U, V = _prep(Q), _prep(K, True, de), _prep(U, True, de), _prep(V, True, de)
+    dO = _prep(dO.to(Q.dtype))
+    R = R.to(torch.float32)
+    if R.stride(-1) != 1:
+        R = R.contiguous()
+    dQ = torch.empty_like(Q, memory_format=torch.contiguous_format)
+    dK, dU, dV = (torch.empty_like(t, memory_format=torch.contiguous_format) for t in (K, U, V))
+    dR = torch.empty((B, H, S, E), dtype=torch.float32, device=Q.device)
+    d = _dims(B, H, S, dh, hk, E, de, Q.dtype)
+    nbytes = int(lib.flashmhf_backward_workspace_bytes(C.byref(d)))
+    ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=Q.device)
+    p = _lib.BwdParams(d, _tensor(Q), _tensor(K), _tensor(U), _tensor(V), _tensor(R), _tensor(dO), _tensor(dQ),
+                       _tensor(dK), _tensor(dU), _tensor(dV), _tensor(dR), ws.data_ptr(), nbytes)
+    with torch.cuda.device(Q.device):
+        _lib.check(lib.flashmhf_backward(C.byref(p), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return dQ, dK, dU, dV, dR
+
+
+class FlashMHFFunction(torch.autograd.Function):
+    """forward(ctx, Q, K, U, V, R) -> O ; backward(ctx, dO) -> dQ, dK, dU, dV, dR."""
+
+    @staticmethod
+    def forward(ctx, Q, K, U, V, R):
+        O = forward_raw(Q, K, U, V, R)
+        ctx.save_for_backward(Q, K, U, V, R)
+        return O
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        Q, K, U, V, R = ctx.saved_tensors
+        dQ, dK, dU, dV, dR = backward_raw(Q, K, U, V, R, grad_output)
+        return dQ, dK, dU, dV, dR.to(R.dtype)
+
+
+def flash_mhf(Q, K, U, V, R):
+    return FlashMHFFunction.apply(Q, K, U, V, R)

@@ -1,0 +1,125 @@
+/*
+ * flashmhf.h -- C ABI of the B200 (sm_100a) FlashMHF multi-head FFN operator
+ *
+ *     O = sum_e R_e * ((SiLU(Q K_e^T) * (Q U_e^T)) V_e)          forward and backward
+ *
+ * Plain pointers and sizes only; no framework types.  Every entry point returns 0 or a negative
+ * flashmhf_status code, never throws, never aborts, never blocks on the stream (except where a
+ * comment says "synchronous").  The caller owns every buffer, including the workspace.
+ *
+ * The entry points stand where the reference's native extension has its two pybind functions,
+ *   flashffn_moe_forward(Q,K,U,V,R,O)                         kernels/thunderkittens/flash_ffn_moe.cu:938-1007
+ *   flashffn_moe_backward(Q,K,U,V,R,dQ,dK,dU,dV,dR,dO)        kernels/thunderkittens/flash_ffn_moe.cu:1012-1133
+ * and where its Triton wrapper launches its three kernels (kernels/triton/flash_mlp_moe.py:777-790,
+ * 832-866).  Shapes follow that wrapper's docstring (flash_mlp_moe.py:745-753):
+ *
+ *   Q, O, dO, dQ : [B, H, S, d_h]        K, U, V, dK, dU, dV : [H_kuv, E, d_e, d_h]
+ *   R, dR        : [B, H, S, E] fp32     H % H_kuv == 0, d_e % 64 == 0, d_h in {64, 96, 128}
+ *
+ * Unlike the reference's R-transposing wrapper (kernels/thunderkittens/flash_ffn_moe_torch.py:9)
+ * R is taken as the model produces it, [B,H,S,E].
+ */
+#ifndef FLASHMHF_H_
+#define FLASHMHF_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FLASHMHF_ABI_VERSION 1
+
+typedef enum flashmhf_status {
+    FLASHMHF_OK = 0,
+    FLASHMHF_ERR_NULL = -1,          /* a required pointer is NULL */
+    FLASHMHF_ERR_BAD_SHAPE = -2,     /* unsupported d_h, d_e % 64 != 0, H % H_kuv != 0, a dim < 1 ... */
+    FLASHMHF_ERR_BAD_DTYPE = -3,     /* dtype is neither FLASHMHF_BF16 nor FLASHMHF_F32_CHECK */
+    FLASHMHF_ERR_BAD_STRIDE = -4,    /* stride not expressible (negative, not a multiple of 16 bytes, E and d_e do not collapse) */
+    FLASHMHF_ERR_MISALIGNED = -5,    /* base pointer not 16-byte aligned */
+    FLASHMHF_ERR_WORKSPACE = -6,     /* workspace NULL or smaller than flashmhf_backward_workspace_bytes() */
+    FLASHMHF_ERR_ARCH = -7,          /* current device is not compute capability 10.x */
+    FLASHMHF_ERR_CUDA = -8,          /* a CUDA runtime/driver call failed (see flashmhf_last_cuda_error) */
+    FLASHMHF_ERR_DEVICE_TIMEOUT = -9 /* a kernel gave up on a bounded wait and returned early (flashmhf_device_status) */
+} flashmhf_status;
+
+typedef enum flashmhf_dtype {
+    FLASHMHF_BF16 = 0,      /* Q,K,U,V,O,dO,dQ,dK,dU,dV bfloat16; tensor-core (tcgen05) kernels, fp32 accumulation */
+    FLASHMHF_F32_CHECK = 1  /* the same tensors float32; CUDA-core check kernels, fp32 throughout (test mode) */
+} flashmhf_dtype;
+
+/* A 4-D tensor whose innermost dimension is contiguous.  stride[i] is the ELEMENT stride of outer
+ * dimension i (for Q: B, H, S; for K: H_kuv, E, d_e; for R: B, H, S).  For the bf16 path every
+ * stride must be a multiple of 8 elements (16 bytes) and the pointer 16-byte aligned; for K/U/V
+ * (and dK/dU/dV) stride[1] must equal d_e * stride[2] so that (E, d_e) is one row index. */
+typedef struct flashmhf_tensor {
+    void *ptr;
+    int64_t stride[3];
+} flashmhf_tensor;
+
+typedef struct flashmhf_dims {
+    int32_t B, H, S, Dh;      /* batch, FFN heads, sequence length, head dim */
+    int32_t Hkuv, E, De;      /* K/U/V heads, sub-networks per head, rows per sub-network */
+    int32_t dtype;            /* flashmhf_dtype */
+} flashmhf_dims;
+
+typedef struct flashmhf_fwd_params {
+    flashmhf_dims d;
+    flashmhf_tensor Q, K, U, V, R; /* inputs */
+    flashmhf_tensor O;             /* output, every element written; no pre-zeroing needed */
+} flashmhf_fwd_params;
+
+typedef struct flashmhf_bwd_params {
+    flashmhf_dims d;
+    flashmhf_tensor Q, K, U, V, R, dO; /* inputs (dO may be a transposed view, like any other tensor here) */
+    flashmhf_tensor dQ, dK, dU, dV, dR; /* outputs, every element written; dR is fp32 */
+    void *workspace;                    /* device scratch, 256-byte aligned, contents undefined on entry and exit */
+    size_t workspace_bytes;
+} flashmhf_bwd_params;
+
+/* ABI version of the loaded library (== FLASHMHF_ABI_VERSION of the header it was built from).
+ * Reference counterpart: none (pybind modules carry no version). */
+int flashmhf_abi_version(void);
+
+/* Static, NUL-terminated description of a status code.
+ * Reference counterpart: the TORCH_CHECK / CHECK_CUDA_ERROR messages, flash_ffn_moe.cu:940-960, 1006. */
+const char *flashmhf_strerror(int status);
+
+/* Text of the last CUDA error this thread's calls met (valid until the next failing call). */
+const char *flashmhf_last_cuda_error(void);
+
+/* Forward.  Enqueues on `stream` (a cudaStream_t; NULL = legacy default stream) of the CURRENT
+ * device and returns.  Replaces flashffn_moe_forward, flash_ffn_moe.cu:938-1007, and the launch at
+ * kernels/triton/flash_mlp_moe.py:777-790. */
+int flashmhf_forward(const flashmhf_fwd_params *p, void *stream);
+
+/* Bytes of scratch flashmhf_backward needs for these dims (0 is possible).  Pure host arithmetic. */
+size_t flashmhf_backward_workspace_bytes(const flashmhf_dims *d);
+
+/* Backward: dQ, dK, dU, dV, dR from dO, recomputing the intermediate.  Enqueues on `stream` and
+ * returns.  Deterministic (no floating-point atomics).  Replaces flashffn_moe_backward,
+ * flash_ffn_moe.cu:1012-1133, and the two launches at kernels/triton/flash_mlp_moe.py:832-866. */
+int flashmhf_backward(const flashmhf_bwd_params *p, void *stream);
+
+/* SYNCHRONOUS.  Waits for the current device, then reads and clears the status word the kernels
+ * write when a bounded wait runs out.  *code = 0 if none did; otherwise a kernel/role identifier,
+ * and the call returns FLASHMHF_ERR_DEVICE_TIMEOUT.  Reference counterpart: none. */
+int flashmhf_device_status(int *code);
+
+/* Profiling aid.  Between flashmhf_profile_begin and flashmhf_profile_end every forward/backward
+ * call records a CUDA event on its stream before its first kernel and after each kernel (no
+ * synchronisation, up to `max_marks` events in total).  flashmhf_profile_end is SYNCHRONOUS: it
+ * waits for the device and returns, for each kernel launched in between, its duration in
+ * milliseconds and a tag (1 forward, 2 backward dQ/dR, 3 backward dK/dU/dV, 4 split reduction).
+ * One profiling session at a time, calls from one stream.  Reference counterpart: none. */
+int flashmhf_profile_begin(int max_marks);
+int flashmhf_profile_end(float *ms, int *tags, int capacity, int *n_out);
+
+/* Number of kernel launches this library has enqueued since it was loaded (all threads). */
+uint64_t flashmhf_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHMHF_H_ */

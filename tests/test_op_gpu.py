@@ -1,0 +1,168 @@
+"""GPU parity: the CUDA operator (through the C ABI) against the CPU oracle on the same seeded inputs.
+
+Tolerances (relative L2 error): fp32 check mode 1e-5; bf16 tensor-core path 1e-2 against the oracle
+evaluated in fp32 on the same bf16-rounded inputs, and 1e-2 against the oracle's bf16 eager evaluation."""
+import pytest
+import torch
+
+from oracle import mhffn_oracle as orc
+from tests.golden_util import load_golden
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-5
+TOL_BF16 = 1e-2
+
+# (B, H, Hkuv, S, dh, E, de)
+SHAPES_SMALL = [
+    (1, 1, 1, 128, 128, 1, 64),
+    (2, 2, 2, 200, 128, 2, 128),    # ragged tail (200 = 128 + 72)
+    (1, 2, 2, 37, 64, 3, 64),       # shorter than one tile
+    (2, 3, 3, 130, 96, 2, 64),      # the 128M model's head dim
+    (1, 4, 2, 256, 128, 2, 64),     # shared K/U/V heads (G = 2)
+    (1, 2, 1, 150, 96, 1, 192),     # G = 2, d_h = 96, single sub-network
+]
+SHAPES_MODEL = [
+    (1, 8, 8, 512, 96, 8, 256),     # 128M layer dims
+    (1, 8, 8, 384, 128, 11, 256),   # 370M layer dims
+    (1, 2, 2, 300, 64, 8, 192),     # operator sweep d_h=64 point
+    (1, 2, 2, 256, 128, 8, 320),    # operator sweep d_h=128 point
+]
+
+
+def _dev(ts):
+    return [t.cuda() for t in ts]
+
+
+def _oracle_grads(Q, K, U, V, R, dO):
+    return orc.mhffn_backward(Q.double(), K.double(), U.double(), V.double(), R.double(), dO.double())
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    from flashmhf_b200 import _lib
+    yield
+    _lib.device_status()  # raises if any kernel gave up on a bounded wait
+
+
+@pytest.mark.parametrize("shape", SHAPES_SMALL)
+def test_check_mode_forward_backward(shape):
+    import flashmhf_b200 as fm
+    B, H, Hk, S, dh, E, de = shape
+    Q, K, U, V, R, dO = orc.make_op_inputs(B, H, S, dh, E, de, Hkuv=Hk, seed=11, dtype=torch.float32)
+    O = fm.forward_raw(*_dev([Q, K, U, V, R])).cpu()
+    assert orc.rel_l2(O, orc.mhffn_forward(Q.double(), K.double(), U.double(), V.double(), R.double())) < TOL_F32
+    got = [g.cpu() for g in fm.backward_raw(*_dev([Q, K, U, V, R, dO]))]
+    for name, a, b in zip("dQ dK dU dV dR".split(), got, _oracle_grads(Q, K, U, V, R, dO)):
+        assert orc.rel_l2(a, b) < TOL_F32, name
+
+
+@pytest.mark.parametrize("shape", SHAPES_SMALL + SHAPES_MODEL)
+def test_bf16_forward(shape):
+    import flashmhf_b200 as fm
+    B, H, Hk, S, dh, E, de = shape
+    Q, K, U, V, R = orc.make_op_inputs(B, H, S, dh, E, de, Hkuv=Hk, seed=12, dtype=torch.bfloat16, with_dO=False)
+    O = fm.forward_raw(*_dev([Q, K, U, V, R])).cpu().float()
+    ref32 = orc.mhffn_forward(Q.float(), K.float(), U.float(), V.float(), R)
+    assert orc.rel_l2(O, ref32) < TOL_BF16
+    assert orc.rel_l2(O, orc.mhffn_forward(Q, K, U, V, R).float()) < TOL_BF16  # the eager path in bf16
+
+
+@pytest.mark.parametrize("shape", SHAPES_SMALL + SHAPES_MODEL)
+def test_bf16_backward(shape):
+    import flashmhf_b200 as fm
+    B, H, Hk, S, dh, E, de = shape
+    Q, K, U, V, R, dO = orc.make_op_inputs(B, H, S, dh, E, de, Hkuv=Hk, seed=13, dtype=torch.bfloat16)
+    got = [g.cpu().float() for g in fm.backward_raw(*_dev([Q, K, U, V, R, dO]))]
+    ref = _oracle_grads(Q.float(), K.float(), U.float(), V.float(), R, dO.float())
+    for name, a, b in zip("dQ dK dU dV dR".split(), got, ref):
+        assert orc.rel_l2(a, b) < TOL_BF16, name
+
+
+def test_autograd_function_matches_oracle_autograd():
+    import flashmhf_b200 as fm
+    Q, K, U, V, R, dO = orc.make_op_inputs(2, 2, 192, 128, 2, 64, seed=14, dtype=torch.bfloat16)
+    ins = [t.cuda().requires_grad_(True) for t in (Q, K, U, V, R)]
+    O = fm.flash_mhf(*ins)
+    (O.float() * dO.cuda().float()).sum().backward()
+    ref = _oracle_grads(Q.float(), K.float(), U.float(), V.float(), R, dO.float())
+    for name, t, b in zip("dQ dK dU dV dR".split(), ins, ref):
+        assert t.grad is not None and t.grad.dtype == t.dtype and t.grad.shape == t.shape
+        assert orc.rel_l2(t.grad.cpu().float(), b) < TOL_BF16, name
+
+
+def test_strided_views_are_read_in_place():
+    """Q and dO as transposed views of [B,S,H,d_h] buffers, weights as views of [I, H*d_h] matrices."""
+    import flashmhf_b200 as fm
+    B, H, S, dh, E, de = 2, 2, 160, 128, 2, 64
+    Q, K, U, V, R, dO = orc.make_op_inputs(B, H, S, dh, E, de, seed=15, dtype=torch.bfloat16)
+    to_view = lambda t: t.cuda().transpose(1, 2).contiguous().transpose(1, 2)         # [B,H,S,dh] view, S-major memory
+    w_view = lambda w: w.cuda().permute(1, 2, 0, 3).reshape(E * de, H * dh).contiguous().view(E, de, H, dh).permute(2, 0, 1, 3)
+    Qv, dOv, Kv, Uv, Vv = to_view(Q), to_view(dO), w_view(K), w_view(U), w_view(V)
+    assert not Qv.is_contiguous() and not Kv.is_contiguous()
+    O = fm.forward_raw(Qv, Kv, Uv, Vv, R.cuda()).cpu().float()
+    assert orc.rel_l2(O, orc.mhffn_forward(Q.float(), K.float(), U.float(), V.float(), R)) < TOL_BF16
+    got = [g.cpu().float() for g in fm.backward_raw(Qv, Kv, Uv, Vv, R.cuda(), dOv)]
+    ref = _oracle_grads(Q.float(), K.float(), U.float(), V.float(), R, dO.float())
+    for name, a, b in zip("dQ dK dU dV dR".split(), got, ref):
+        assert orc.rel_l2(a, b) < TOL_BF16, name
+
+
+@pytest.mark.parametrize("name", ["layer_tiny_dh64", "layer_tiny_gqa"])
+def test_golden_operator_fixture(name):
+    """The operands the reference hands to its flash back-end, and the O its eager path gives for them."""
+    import flashmhf_b200 as fm
+    d = load_golden(name)
+    ops = [d["op_" + k] for k in "QKUVR"]
+    O32 = fm.forward_raw(*_dev(ops)).cpu()
+    assert orc.rel_l2(O32, d["op_O"]) < TOL_F32
+    ops16 = [t.to(torch.bfloat16) for t in ops[:4]] + [ops[4]]
+    O16 = fm.forward_raw(*_dev(ops16)).cpu().float()
+    assert orc.rel_l2(O16, d["op_O"]) < TOL_BF16
+
+
+def test_deterministic_bitwise():
+    import flashmhf_b200 as fm
+    ins = _dev(orc.make_op_inputs(2, 2, 300, 128, 3, 128, seed=16, dtype=torch.bfloat16))
+    a = [fm.forward_raw(*ins[:5])] + list(fm.backward_raw(*ins))
+    b = [fm.forward_raw(*ins[:5])] + list(fm.backward_raw(*ins))
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+def test_outputs_fully_written_over_poison():
+    """Every element of O is written even when the buffer starts as NaN (no pre-zeroing contract)."""
+    import flashmhf_b200 as fm
+    Q, K, U, V, R = _dev(orc.make_op_inputs(1, 2, 77, 64, 2, 64, seed=17, dtype=torch.bfloat16, with_dO=False))
+    out = torch.full_like(Q, float("nan"))
+    fm.forward_raw(Q, K, U, V, R, out=out)
+    assert torch.isfinite(out.float()).all()
+
+
+def test_argument_errors_are_python_exceptions():
+    import flashmhf_b200 as fm
+    Q, K, U, V, R = _dev(orc.make_op_inputs(1, 2, 64, 64, 2, 64, seed=18, dtype=torch.bfloat16, with_dO=False))
+    with pytest.raises(TypeError):
+        fm.forward_raw(Q.half(), K, U, V, R)
+    with pytest.raises(ValueError):
+        fm.forward_raw(Q, K[:, :, :32], U[:, :, :32], V[:, :, :32], R)
+    with pytest.raises(ValueError):
+        fm.forward_raw(Q[..., :32], K[..., :32], U[..., :32], V[..., :32], R)
+    with pytest.raises(ValueError):
+        fm.forward_raw(Q.cpu(), K.cpu(), U.cpu(), V.cpu(), R.cpu())
+
+
+def test_large_shape_linearity_property():
+    """At the 370M layer's full token count: O is linear in R, so O(R1) + O(R2) == O(R1 + R2) up to bf16 rounding,
+    and a tile-aligned slice of a big batch equals the same rows computed alone (bitwise)."""
+    import flashmhf_b200 as fm
+    B, H, S, dh, E, de = 4, 8, 2048, 128, 11, 256
+    g = torch.Generator(device="cuda").manual_seed(19)
+    Q = torch.randn(B, H, S, dh, device="cuda", generator=g).bfloat16()
+    K, U, V = (torch.randn(H, E, de, dh, device="cuda", generator=g).mul(0.02).bfloat16() for _ in range(3))
+    R1 = torch.rand(B, H, S, E, device="cuda", generator=g)
+    R2 = torch.rand(B, H, S, E, device="cuda", generator=g)
+    O1, O2, O12 = (fm.forward_raw(Q, K, U, V, r).float() for r in (R1, R2, R1 + R2))
+    assert orc.rel_l2((O1 + O2).cpu(), O12.cpu()) < TOL_BF16
+    sub = fm.forward_raw(Q[1:2, :, 256:1280].contiguous(), K, U, V, R1[1:2, :, 256:1280].contiguous())
+    assert torch.equal(sub, fm.forward_raw(Q, K, U, V, R1)[1:2, :, 256:1280])
