@@ -10,10 +10,12 @@ LIB_PATH = os.path.join(_PKG, "lib", "libflashmhf_b200.so")
 ABI_VERSION = 1
 
 BF16, F32_CHECK = 0, 1
+STATIC_SCRATCH_BYTES = 72 << 20
 
 EXPORTS = ("flashmhf_abi_version", "flashmhf_strerror", "flashmhf_last_cuda_error", "flashmhf_forward",
            "flashmhf_backward_workspace_bytes", "flashmhf_backward", "flashmhf_device_status",
-           "flashmhf_launch_count", "flashmhf_profile_begin", "flashmhf_profile_end")
+           "flashmhf_launch_count", "flashmhf_profile_begin", "flashmhf_profile_end",
+           "flashmhf_backward_static_scratch")
 
 
 class Tensor(C.Structure):
@@ -67,6 +69,8 @@ def load():
         lib.flashmhf_backward_workspace_bytes.argtypes = [C.POINTER(Dims)]
         lib.flashmhf_backward.restype = C.c_int
         lib.flashmhf_backward.argtypes = [C.POINTER(BwdParams), C.c_void_p]
+        lib.flashmhf_backward_static_scratch.restype = C.c_int
+        lib.flashmhf_backward_static_scratch.argtypes = [C.POINTER(BwdParams), C.c_void_p]
         lib.flashmhf_device_status.restype = C.c_int
         lib.flashmhf_device_status.argtypes = [C.POINTER(C.c_int)]
         lib.flashmhf_launch_count.restype = C.c_uint64

@@ -109,6 +109,8 @@ const char *flashmhf_strerror(int status) {
         case FLASHMHF_ERR_ARCH: return "current device is not compute capability 10.x (B200)";
         case FLASHMHF_ERR_CUDA: return "CUDA call failed (see flashmhf_last_cuda_error)";
         case FLASHMHF_ERR_DEVICE_TIMEOUT: return "a kernel gave up on a bounded wait";
+        case FLASHMHF_ERR_SCRATCH_LIMIT:
+            return "these dims need more scratch than the library's built-in 72 MiB array; use flashmhf_backward with a workspace";
         default: return "unknown status";
     }
 }
@@ -170,6 +172,22 @@ int flashmhf_backward(const flashmhf_bwd_params *p, void *stream) {
     } else {
         rc = tc_backward(*p, st, &n);
     }
+    g_launches += (uint64_t)n;
+    return rc;
+}
+
+int flashmhf_backward_static_scratch(const flashmhf_bwd_params *p, void *stream) {
+    if (!p) return FLASHMHF_ERR_NULL;
+    int rc = check_dims(p->d);
+    if (rc) return rc;
+    if (p->d.dtype != FLASHMHF_BF16) return FLASHMHF_ERR_BAD_DTYPE;
+    const flashmhf_tensor *ts[] = {&p->Q, &p->K, &p->U, &p->V, &p->R, &p->dO, &p->dQ, &p->dK, &p->dU, &p->dV, &p->dR};
+    for (const flashmhf_tensor *t : ts)
+        if ((rc = check_tensor(*t)) != 0) return rc;
+    if ((rc = check_arch()) != 0) return rc;
+    if (!device_status_ptr()) return FLASHMHF_ERR_CUDA;
+    int n = 0;
+    rc = tc_backward_static_scratch(*p, static_cast<cudaStream_t>(stream), &n);
     g_launches += (uint64_t)n;
     return rc;
 }

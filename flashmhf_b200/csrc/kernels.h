@@ -19,6 +19,7 @@ cudaError_t simt_backward(const flashmhf_bwd_params &p, cudaStream_t st, int *n_
 int tc_forward(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch);
 int tc_backward(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch);
 size_t tc_backward_workspace_bytes(const flashmhf_dims &d);
+int tc_backward_static_scratch(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch);
 
 void set_cuda_error(cudaError_t e, const char *where);
 

@@ -20,6 +20,8 @@
 //
 // Both use 384 threads: warp 0 TMA producer, warp 1 MMA issuer and tensor-memory owner, warps 4-11
 // element-wise math (warp % 4 = TMEM lane quarter, (warp-4)/4 = which 32 of the 64 block columns).
+#include <mutex>
+
 #include "kernels.h"
 #include "tc_common.cuh"
 #include "tensormap.cuh"
@@ -701,6 +703,54 @@ int launch_bwd(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch) {
 size_t tc_backward_workspace_bytes(const flashmhf_dims &d) {
     const DwPlan pl = dw_plan(d);
     return (size_t)pl.nsplit * 3 * (size_t)d.Hkuv * (size_t)d.E * d.De * d.Dh * sizeof(float);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Built-in scratch for flashmhf_backward_static_scratch: the split partial sums of dK/dU/dV live in
+// this file-scope device array instead of a caller-provided workspace.  One copy per GPU that loads
+// the library, held until the process exits.  The dK/dU/dV kernel writes every partial it later
+// reads, so nothing here has to start at zero.
+constexpr size_t kStaticScratchBytes = FLASHMHF_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mu;
+void *g_scratch_addr[kMaxDevices] = {nullptr};
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address: the
+// address is looked up once per device, with that device current, and cached.
+int static_scratch_ptr(void **out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_cuda_error(e, "cudaGetDevice (static scratch)");
+        return FLASHMHF_ERR_CUDA;
+    }
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    if (!g_scratch_addr[dev]) {
+        void *ptr = nullptr;
+        e = cudaGetSymbolAddress((void **)&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr) {
+            set_cuda_error(e, "cudaGetSymbolAddress(g_static_scratch)");
+            return FLASHMHF_ERR_CUDA;
+        }
+        g_scratch_addr[dev] = ptr;
+    }
+    *out = g_scratch_addr[dev];
+    return FLASHMHF_OK;
+}
+}  // namespace
+
+int tc_backward_static_scratch(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch) {
+    if (tc_backward_workspace_bytes(p.d) > kStaticScratchBytes) return FLASHMHF_ERR_SCRATCH_LIMIT;
+    void *ptr = nullptr;
+    const int rc = static_scratch_ptr(&ptr);
+    if (rc != FLASHMHF_OK) return rc;
+    flashmhf_bwd_params q = p;
+    q.workspace = ptr;
+    q.workspace_bytes = kStaticScratchBytes;
+    return tc_backward(q, st, n_launch);
 }
 
 int tc_backward(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch) {

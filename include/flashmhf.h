@@ -41,7 +41,8 @@ typedef enum flashmhf_status {
     FLASHMHF_ERR_WORKSPACE = -6,     /* workspace NULL or smaller than flashmhf_backward_workspace_bytes() */
     FLASHMHF_ERR_ARCH = -7,          /* current device is not compute capability 10.x */
     FLASHMHF_ERR_CUDA = -8,          /* a CUDA runtime/driver call failed (see flashmhf_last_cuda_error) */
-    FLASHMHF_ERR_DEVICE_TIMEOUT = -9 /* a kernel gave up on a bounded wait and returned early (flashmhf_device_status) */
+    FLASHMHF_ERR_DEVICE_TIMEOUT = -9, /* a kernel gave up on a bounded wait and returned early (flashmhf_device_status) */
+    FLASHMHF_ERR_SCRATCH_LIMIT = -10  /* flashmhf_backward_static_scratch: these dims need more than FLASHMHF_STATIC_SCRATCH_BYTES */
 } flashmhf_status;
 
 typedef enum flashmhf_dtype {
@@ -101,6 +102,29 @@ size_t flashmhf_backward_workspace_bytes(const flashmhf_dims *d);
  * returns.  Deterministic (no floating-point atomics).  Replaces flashffn_moe_backward,
  * flash_ffn_moe.cu:1012-1133, and the two launches at kernels/triton/flash_mlp_moe.py:832-866. */
 int flashmhf_backward(const flashmhf_bwd_params *p, void *stream);
+
+/* Size of the scratch array built into the library for flashmhf_backward_static_scratch: 72 MiB
+ * (enough for the 370M layer shape, H_kuv=8, E*d_e=2816, d_h=128, with its two-way token split). */
+#define FLASHMHF_STATIC_SCRATCH_BYTES (72u << 20)
+
+/* Backward for callers that cannot hand over a workspace and must not trigger an allocation: a host
+ * runtime that gave all device memory to its own planner at start-up (so a cudaMalloc would fail or
+ * stall -- cudaMalloc and cudaFree synchronise the whole device), or one that binds this ABI over
+ * an FFI and has no device allocator to offer.  Same kernels, same results and same argument rules
+ * as flashmhf_backward, but `workspace` / `workspace_bytes` are ignored: the partial sums of dK, dU
+ * and dV go to a static array inside the library (FLASHMHF_STATIC_SCRATCH_BYTES per GPU that loads
+ * the library, held until the process exits).  The caller still passes every input and output.
+ *   - bf16 only.  Dims whose flashmhf_backward_workspace_bytes() exceeds the array are refused
+ *     with FLASHMHF_ERR_SCRATCH_LIMIT; nothing is launched.
+ *   - The call makes no cudaMalloc, cudaFree or other allocating call.  Its FIRST call on a device
+ *     looks up the array's device address (once per device, with that device current); make that
+ *     first call before any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  The
+ *     kernels overwrite everything they later read, so stale contents are harmless, but two calls
+ *     whose kernels overlap on the GPU (different streams, no ordering between them) race on it:
+ *     order them, or use flashmhf_backward with separate workspaces.
+ * This entry point has no counterpart in the reference. */
+int flashmhf_backward_static_scratch(const flashmhf_bwd_params *p, void *stream);
 
 /* SYNCHRONOUS.  Waits for the current device, then reads and clears the status word the kernels
  * write when a bounded wait runs out.  *code = 0 if none did; otherwise a kernel/role identifier,
