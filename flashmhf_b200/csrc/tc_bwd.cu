@@ -35,20 +35,25 @@ constexpr uint32_t kTile = kBT * 128;    // one 128-row x 64-col SW128 chunk: 16
 constexpr uint32_t kWChunk = kBI * 128;  // one 64-row x 64-col chunk: 8 KB
 constexpr int kNumSMs = 148;
 
-// Element-wise backward math for one (token, intermediate column) pair.
-struct BwdElem {
-    float dm, dn, a, dr;
+// Element-wise backward math for two neighbouring intermediate columns of one token row, on packed
+// fp32 pairs.  With t = tanh(m/2): sg = sigmoid(m) = 0.5 + 0.5 t, 1 - sg = 0.5 - 0.5 t, s = m*sg,
+// silu'(m) = sg + s*(1 - sg).
+struct BwdPair {
+    f32x2 dm, dn, sn, da;  // dM, dN, s*N (times r gives A, times dA sums to dR), dA
 };
-__device__ __forceinline__ BwdElem bwd_elem(float m, float n, float da, float r) {
-    const float sg = fast_sigmoid(m);
-    const float s = m * sg;
-    const float sn = s * n;
-    const float t = da * r;
-    BwdElem o;
-    o.dr = da * sn;
-    o.a = sn * r;
-    o.dn = t * s;
-    o.dm = t * n * (fmaf(-s, sg, s) + sg);  // silu'(m) = sg + s*(1-sg)
+__device__ __forceinline__ BwdPair bwd_pair(f32x2 m, f32x2 n, f32x2 da, f32x2 r2) {
+    const f32x2 half = f2_pack(0.5f, 0.5f), nhalf = f2_pack(-0.5f, -0.5f);
+    const f32x2 t = f2_tanh(f2_mul(m, half));
+    const f32x2 sg = f2_fma(t, half, half);
+    const f32x2 omsg = f2_fma(t, nhalf, half);
+    const f32x2 s = f2_mul(m, sg);
+    const f32x2 dsilu = f2_fma(s, omsg, sg);
+    const f32x2 dar = f2_mul(da, r2);
+    BwdPair o;
+    o.sn = f2_mul(s, n);
+    o.dn = f2_mul(dar, s);
+    o.dm = f2_mul(f2_mul(dar, n), dsilu);
+    o.da = da;
     return o;
 }
 
@@ -212,19 +217,21 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const float *rrow = args.R + (long long)b * args.r_sb + (long long)h * args.r_sh + (long long)t * args.r_ss;
         float *drrow = args.dR + (long long)b * args.dr_sb + (long long)h * args.dr_sh + (long long)t * args.dr_ss;
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-        float r_cur = 0.f, r_next = in_range ? __ldg(rrow) : 0.f, dr_acc = 0.f;
+        float r_cur = 0.f, r_next = in_range ? __ldg(rrow) : 0.f;
+        f32x2 dr2 = f2_pack(0.f, 0.f);  // running dR_e of this thread's columns (two interleaved partial sums)
         bool ok = true;
         for (int j = 0; j < nblk; ++j) {
             const int bb = j & 1, nb = j >> 1, e = j / bpe;
             if (j % bpe == 0) {
                 r_cur = r_next;
                 r_next = (in_range && e + 1 < args.E) ? __ldg(rrow + e + 1) : 0.f;
-                dr_acc = 0.f;
+                dr2 = f2_pack(0.f, 0.f);
             }
             if (!mbar_wait(bar(DQ_SFULL + bb), nb & 1, ctl, W + 7)) { ok = false; break; }
             tc_fence_after();
             const uint32_t tS = lane_base + kColS0 + bb * kBufStride + half * 32;
             uint32_t pm[16], pn[16];  // packed bf16 pairs of dM, dN for this thread's 32 columns
+            const f32x2 r2 = f2_pack(r_cur, r_cur);
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
                 uint32_t m[16], n[16], da[16];
@@ -234,13 +241,11 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 tmem_ld_wait();
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const BwdElem x0 = bwd_elem(__uint_as_float(m[2 * i]), __uint_as_float(n[2 * i]),
-                                                __uint_as_float(da[2 * i]), r_cur);
-                    const BwdElem x1 = bwd_elem(__uint_as_float(m[2 * i + 1]), __uint_as_float(n[2 * i + 1]),
-                                                __uint_as_float(da[2 * i + 1]), r_cur);
-                    dr_acc += x0.dr + x1.dr;
-                    pm[sub * 8 + i] = pack_bf16(x0.dm, x1.dm);
-                    pn[sub * 8 + i] = pack_bf16(x0.dn, x1.dn);
+                    const BwdPair x = bwd_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]), f2_pack_bits(n[2 * i], n[2 * i + 1]),
+                                               f2_pack_bits(da[2 * i], da[2 * i + 1]), r2);
+                    dr2 = f2_fma(x.da, x.sn, dr2);
+                    pm[sub * 8 + i] = f2_to_bf16x2(x.dm);
+                    pn[sub * 8 + i] = f2_to_bf16x2(x.dn);
                 }
             }
             tc_fence_before();
@@ -256,6 +261,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             mbar_arrive(bar(DQ_PFULL));
             if ((j + 1) % bpe == 0) {  // sub-network finished: add the two column halves of dR_e
                 const int xb = e & 1;
+                float dr_lo, dr_hi;
+                f2_unpack(dr2, dr_lo, dr_hi);
+                const float dr_acc = dr_lo + dr_hi;
                 if (half == 1) {
                     drx[xb * 128 + row] = dr_acc;
                     mbar_arrive(bar(DQ_DRFULL + xb));
@@ -490,6 +498,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             if (!mbar_wait(bar(DW_SFULL), i & 1, ctl, W + 7)) { ok = false; break; }
             tc_fence_after();
             uint32_t pm[16], pn[16], pa[16];
+            const f32x2 r2 = f2_pack(r, r);
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
                 uint32_t m[16], n[16], da[16];
@@ -500,13 +509,11 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 tmem_ld_wait();
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
-                    const BwdElem x0 = bwd_elem(__uint_as_float(m[2 * q]), __uint_as_float(n[2 * q]),
-                                                __uint_as_float(da[2 * q]), r);
-                    const BwdElem x1 = bwd_elem(__uint_as_float(m[2 * q + 1]), __uint_as_float(n[2 * q + 1]),
-                                                __uint_as_float(da[2 * q + 1]), r);
-                    pm[sub * 8 + q] = pack_bf16(x0.dm, x1.dm);
-                    pn[sub * 8 + q] = pack_bf16(x0.dn, x1.dn);
-                    pa[sub * 8 + q] = pack_bf16(x0.a, x1.a);
+                    const BwdPair x = bwd_pair(f2_pack_bits(m[2 * q], m[2 * q + 1]), f2_pack_bits(n[2 * q], n[2 * q + 1]),
+                                               f2_pack_bits(da[2 * q], da[2 * q + 1]), r2);
+                    pm[sub * 8 + q] = f2_to_bf16x2(x.dm);
+                    pn[sub * 8 + q] = f2_to_bf16x2(x.dn);
+                    pa[sub * 8 + q] = f2_to_bf16x2(f2_mul(x.sn, r2));
                 }
             }
             tc_fence_before();

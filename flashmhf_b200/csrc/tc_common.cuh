@@ -208,6 +208,57 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
+// Packed pairs of fp32 in one 64-bit register: sm_100 executes mul/fma/add on both halves with one
+// instruction, which halves the issue slots the element-wise math needs.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ f32x2 f2_pack_bits(uint32_t lo, uint32_t hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(f32x2 v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 f2_tanh(f32x2 v) {
+    float a, b;
+    f2_unpack(v, a, b);
+    return f2_pack(fast_tanh(a), fast_tanh(b));
+}
+__device__ __forceinline__ uint32_t f2_to_bf16x2(f32x2 v) {
+    float a, b;
+    f2_unpack(v, a, b);
+    return pack_bf16(a, b);
+}
+
+// Forward activation for two neighbouring columns: bf16x2 of  m * sigmoid(m) * n * r.
+// With t = tanh(m/2): m*sigmoid(m)*n*r = p + p*t, p = (m*n) * (r/2).   `half_r` = (r/2, r/2).
+__device__ __forceinline__ uint32_t fwd_act_pair(f32x2 m, f32x2 n, f32x2 half_r) {
+    const f32x2 half = f2_pack(0.5f, 0.5f);
+    const f32x2 t = f2_tanh(f2_mul(m, half));
+    const f32x2 p = f2_mul(f2_mul(m, n), half_r);
+    return f2_to_bf16x2(f2_fma(p, t, p));
+}
+
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }

@@ -193,14 +193,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             tc_fence_before();
             mbar_arrive(bar(BAR_SEMPTY + bb));
             uint32_t a[16];
+            const f32x2 half_r = f2_pack(0.5f * r_cur, 0.5f * r_cur);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float m0 = __uint_as_float(m[2 * i]), m1 = __uint_as_float(m[2 * i + 1]);
-                const float n0 = __uint_as_float(n[2 * i]), n1 = __uint_as_float(n[2 * i + 1]);
-                const float a0 = m0 * fast_sigmoid(m0) * (n0 * r_cur);
-                const float a1 = m1 * fast_sigmoid(m1) * (n1 * r_cur);
-                a[i] = pack_bf16(a0, a1);
-            }
+            for (int i = 0; i < 16; ++i)
+                a[i] = fwd_act_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]), f2_pack_bits(n[2 * i], n[2 * i + 1]), half_r);
             if (!mbar_wait(bar(BAR_AEMPTY + bb), (nb & 1) ^ 1, ctl, W + 7)) { ok = false; break; }
             const uint32_t arow = sA + bb * L::kABytes;
 #pragma unroll
