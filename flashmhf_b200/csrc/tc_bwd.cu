@@ -147,67 +147,82 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 tma_load_4d(sQ + c * kTile, &tmQ, bar(DQ_QFULL), c * 64, t0, h, b);
                 tma_load_4d(sdO + c * kTile, &tmdO, bar(DQ_QFULL), c * 64, t0, h, b);
             }
+            int sk = 0, sv = 0;
+            uint32_t phk = 1, phv = 1;
             for (int j = 0; j < nblk; ++j) {
-                const int sk = j % L::kKUStages, nk = j / L::kKUStages, sv = j % L::kVStages, nv = j / L::kVStages;
                 const int row = j * kBI;
-                if (!mbar_wait(bar(DQ_KUEMPTY + sk), (nk & 1) ^ 1, ctl, W + 1)) break;
-                mbar_arrive_expect_tx(bar(DQ_KUFULL + sk), L::kKUStage);
+                if (!mbar_wait(bar(DQ_KUEMPTY + sk), phk, ctl, W + 1)) break;
+                const uint32_t fk = bar(DQ_KUFULL + sk);
+                mbar_arrive_expect_tx(fk, L::kKUStage);
+#pragma unroll
                 for (int c = 0; c < L::kChunks; ++c) {
                     const uint32_t d = sKU + sk * L::kKUStage + c * 2 * kWChunk;
-                    tma_load_3d(d, &tmK, bar(DQ_KUFULL + sk), c * 64, row, hk);
-                    tma_load_3d(d + kWChunk, &tmU, bar(DQ_KUFULL + sk), c * 64, row, hk);
+                    tma_load_3d(d, &tmK, fk, c * 64, row, hk);
+                    tma_load_3d(d + kWChunk, &tmU, fk, c * 64, row, hk);
                 }
-                if (!mbar_wait(bar(DQ_VEMPTY + sv), (nv & 1) ^ 1, ctl, W + 2)) break;
-                mbar_arrive_expect_tx(bar(DQ_VFULL + sv), L::kVStage);
+                if (!mbar_wait(bar(DQ_VEMPTY + sv), phv, ctl, W + 2)) break;
+                const uint32_t fv = bar(DQ_VFULL + sv);
+                mbar_arrive_expect_tx(fv, L::kVStage);
+#pragma unroll
                 for (int c = 0; c < L::kChunks; ++c)
-                    tma_load_3d(sV + sv * L::kVStage + c * kWChunk, &tmV, bar(DQ_VFULL + sv), c * 64, row, hk);
+                    tma_load_3d(sV + sv * L::kVStage + c * kWChunk, &tmV, fv, c * 64, row, hk);
+                if (++sk == L::kKUStages) { sk = 0; phk ^= 1; }
+                if (++sv == L::kVStages) { sv = 0; phv ^= 1; }
             }
         }
     } else if (warp == 1) {
+        // One thread issues every MMA: descriptors are built once and advanced by constants.
         if (lane == 0) {
             constexpr uint32_t idS = umma_idesc(128, 2 * kBI, false, false);  // S  = Q  [K;U]^T
             constexpr uint32_t idA = umma_idesc(128, kBI, false, false);      // dA = dO V^T
             constexpr uint32_t idQ = umma_idesc(128, DH, false, true);        // dQ += [dM|dN] [K;U]
-            auto gemm3 = [&](int jj) -> bool {
-                const int sk = jj % L::kKUStages;
-                if (!mbar_wait(bar(DQ_PFULL), jj & 1, ctl, W + 6)) return false;
+            const uint64_t dQd = desc_kmajor(sQ), dOd = desc_kmajor(sdO), dKU0 = desc_kmajor(sKU), dV0 = desc_kmajor(sV),
+                           dP = desc_kmajor(sP), dKUmn0 = desc_mnmajor(sKU, 2 * kWChunk);
+            constexpr uint64_t kKUStep = L::kKUStage >> 4, kVStep = L::kVStage >> 4;
+            auto gemm3 = [&](int sk, uint32_t p_parity, bool first) -> bool {
+                if (!mbar_wait(bar(DQ_PFULL), p_parity, ctl, W + 6)) return false;
                 tc_fence_after();
-                const uint32_t ku = sKU + sk * L::kKUStage;
+                const uint64_t dku = dKUmn0 + sk * kKUStep;
 #pragma unroll
                 for (int k = 0; k < 8; ++k)  // K = 128: 64 columns of dM (rows of K) then 64 of dN (rows of U)
-                    umma_ss(tmem + kColAcc, desc_kmajor(sP + (k >> 2) * kTile + (k & 3) * 32),
-                            desc_mnmajor(ku + k * 2048, 2 * kWChunk), idQ, (jj > 0 || k > 0) ? 1u : 0u);
+                    umma_ss(tmem + kColAcc, dP + (((k >> 2) * kTile + (k & 3) * 32) >> 4), dku + k * 128, idQ,
+                            (!first || k > 0) ? 1u : 0u);
                 umma_commit(bar(DQ_KUEMPTY + sk));
                 umma_commit(bar(DQ_PEMPTY));
                 return true;
             };
             bool ok = mbar_wait(bar(DQ_QFULL), 0, ctl, W + 3);
+            int sk = 0, sv = 0, sk_prev = 0;
+            uint32_t phk = 0, phv = 0;
             for (int j = 0; ok && j < nblk; ++j) {
-                const int sk = j % L::kKUStages, nk = j / L::kKUStages, sv = j % L::kVStages, nv = j / L::kVStages;
-                const int bb = j & 1, nb = j >> 1;
-                if (!mbar_wait(bar(DQ_KUFULL + sk), nk & 1, ctl, W + 4)) { ok = false; break; }
-                if (!mbar_wait(bar(DQ_VFULL + sv), nv & 1, ctl, W + 4)) { ok = false; break; }
-                if (!mbar_wait(bar(DQ_SEMPTY + bb), (nb & 1) ^ 1, ctl, W + 5)) { ok = false; break; }
+                const int bb = j & 1;
+                const uint32_t ph_b = (j >> 1) & 1;
+                if (!mbar_wait(bar(DQ_KUFULL + sk), phk, ctl, W + 4)) { ok = false; break; }
+                if (!mbar_wait(bar(DQ_VFULL + sv), phv, ctl, W + 4)) { ok = false; break; }
+                if (!mbar_wait(bar(DQ_SEMPTY + bb), ph_b ^ 1, ctl, W + 5)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t ku = sKU + sk * L::kKUStage, vv = sV + sv * L::kVStage;
+                const uint64_t dku = dKU0 + sk * kKUStep, dv = dV0 + sv * kVStep;
                 const uint32_t tS = tmem + kColS0 + bb * kBufStride;
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const int c = k >> 2, kk = k & 3;
-                    umma_ss(tS, desc_kmajor(sQ + c * kTile + kk * 32), desc_kmajor(ku + c * 2 * kWChunk + kk * 32), idS,
+                    umma_ss(tS, dQd + ((c * kTile + kk * 32) >> 4), dku + ((c * 2 * kWChunk + kk * 32) >> 4), idS,
                             k > 0 ? 1u : 0u);
                 }
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const int c = k >> 2, kk = k & 3;
-                    umma_ss(tS + kColdA, desc_kmajor(sdO + c * kTile + kk * 32), desc_kmajor(vv + c * kWChunk + kk * 32),
-                            idA, k > 0 ? 1u : 0u);
+                    umma_ss(tS + kColdA, dOd + ((c * kTile + kk * 32) >> 4), dv + ((c * kWChunk + kk * 32) >> 4), idA,
+                            k > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(DQ_VEMPTY + sv));
                 umma_commit(bar(DQ_SFULL + bb));
-                if (j > 0) ok = gemm3(j - 1);
+                if (j > 0) ok = gemm3(sk_prev, (j - 1) & 1, j == 1);
+                sk_prev = sk;
+                if (++sk == L::kKUStages) { sk = 0; phk ^= 1; }
+                if (++sv == L::kVStages) { sv = 0; phv ^= 1; }
             }
-            if (ok) ok = gemm3(nblk - 1);
+            if (ok) ok = gemm3(sk_prev, (nblk - 1) & 1, nblk == 1);
             umma_commit(bar(DQ_ACCFULL));
         }
     } else if (warp >= 4) {
@@ -220,9 +235,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         float r_cur = 0.f, r_next = in_range ? __ldg(rrow) : 0.f;
         f32x2 dr2 = f2_pack(0.f, 0.f);  // running dR_e of this thread's columns (two interleaved partial sums)
         bool ok = true;
+        int in_e = 0, e = 0;  // block index inside the current sub-network; current sub-network
         for (int j = 0; j < nblk; ++j) {
-            const int bb = j & 1, nb = j >> 1, e = j / bpe;
-            if (j % bpe == 0) {
+            const int bb = j & 1, nb = j >> 1;
+            if (in_e == 0) {
                 r_cur = r_next;
                 r_next = (in_range && e + 1 < args.E) ? __ldg(rrow + e + 1) : 0.f;
                 dr2 = f2_pack(0.f, 0.f);
@@ -259,7 +275,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
             fence_async_smem();
             mbar_arrive(bar(DQ_PFULL));
-            if ((j + 1) % bpe == 0) {  // sub-network finished: add the two column halves of dR_e
+            if (++in_e == bpe) {  // sub-network finished: add the two column halves of dR_e
                 const int xb = e & 1;
                 float dr_lo, dr_hi;
                 f2_unpack(dr2, dr_lo, dr_hi);
@@ -271,6 +287,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     if (!mbar_wait(bar(DQ_DRFULL + xb), (e >> 1) & 1, ctl, W + 9)) { ok = false; break; }
                     if (in_range) drrow[e] = dr_acc + drx[xb * 128 + row];
                 }
+                in_e = 0;
+                ++e;
             }
         }
         if (ok) ok = mbar_wait(bar(DQ_ACCFULL), 0, ctl, W + 10);
@@ -412,65 +430,75 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 tma_load_3d(sW + c * 2 * kWChunk + kWChunk, &tmU, bar(DW_WFULL), c * 64, row, hk);
                 tma_load_3d(sW + L::kOffWV + c * kWChunk, &tmV, bar(DW_WFULL), c * 64, row, hk);
             }
+            int st = 0;
+            uint32_t ph = 1;
             for (int i = 0; i < ntiles; ++i) {
-                const int s = i % L::kTokStages, n = i / L::kTokStages;
                 int ts, hh, bb;
                 tile_coords(i, ts, hh, bb);
-                if (!mbar_wait(bar(DW_TEMPTY + s), (n & 1) ^ 1, ctl, W + 1)) break;
-                mbar_arrive_expect_tx(bar(DW_TFULL + s), L::kTokStage);
-                const uint32_t d = sTok + s * L::kTokStage;
+                if (!mbar_wait(bar(DW_TEMPTY + st), ph, ctl, W + 1)) break;
+                const uint32_t fb = bar(DW_TFULL + st);
+                mbar_arrive_expect_tx(fb, L::kTokStage);
+                const uint32_t d = sTok + st * L::kTokStage;
+#pragma unroll
                 for (int c = 0; c < L::kChunks; ++c) {
-                    tma_load_4d(d + c * kTile, &tmQ, bar(DW_TFULL + s), c * 64, ts * kBT, hh, bb);
-                    tma_load_4d(d + (L::kChunks + c) * kTile, &tmdO, bar(DW_TFULL + s), c * 64, ts * kBT, hh, bb);
+                    tma_load_4d(d + c * kTile, &tmQ, fb, c * 64, ts * kBT, hh, bb);
+                    tma_load_4d(d + (L::kChunks + c) * kTile, &tmdO, fb, c * 64, ts * kBT, hh, bb);
                 }
+                if (++st == L::kTokStages) { st = 0; ph ^= 1; }
             }
         }
     } else if (warp == 1) {
+        // One thread issues every MMA: descriptors are built once and advanced by constants.
         if (lane == 0) {
             constexpr uint32_t idS = umma_idesc(128, 2 * kBI, false, false);  // S  = Q  [K;U]^T
             constexpr uint32_t idA = umma_idesc(128, kBI, false, false);      // dA = dO V^T
             constexpr uint32_t idKU = umma_idesc(128, DH, true, true);        // [dK;dU] += [dM|dN]^T Q
             constexpr uint32_t idV = umma_idesc(64, DH, true, true);          // dV      += A^T dO
-            auto gemm34 = [&](int ii) -> bool {
-                const int s = ii % L::kTokStages;
-                if (!mbar_wait(bar(DW_PFULL), ii & 1, ctl, W + 6)) return false;
+            const uint64_t dQk0 = desc_kmajor(sTok), dGk0 = desc_kmajor(sTok + L::kChunks * kTile),
+                           dQmn0 = desc_mnmajor(sTok, kTile), dGmn0 = desc_mnmajor(sTok + L::kChunks * kTile, kTile),
+                           dKU = desc_kmajor(sW), dV = desc_kmajor(sW + L::kOffWV), dPmn = desc_mnmajor(sP, kTile),
+                           dAmn = desc_mnmajor(sA, kTile);
+            constexpr uint64_t kTokStep = L::kTokStage >> 4;
+            auto gemm34 = [&](int st, uint32_t p_parity, bool first) -> bool {
+                if (!mbar_wait(bar(DW_PFULL), p_parity, ctl, W + 6)) return false;
                 tc_fence_after();
-                const uint32_t q0 = sTok + s * L::kTokStage, g0 = q0 + L::kChunks * kTile;
+                const uint64_t dq = dQmn0 + st * kTokStep, dg = dGmn0 + st * kTokStep;
 #pragma unroll
                 for (int k = 0; k < kBT / 16; ++k)
-                    umma_ss(tmem + kColKU, desc_mnmajor(sP + k * 2048, kTile), desc_mnmajor(q0 + k * 2048, kTile), idKU,
-                            (ii > 0 || k > 0) ? 1u : 0u);
+                    umma_ss(tmem + kColKU, dPmn + k * 128, dq + k * 128, idKU, (!first || k > 0) ? 1u : 0u);
 #pragma unroll
                 for (int k = 0; k < kBT / 16; ++k)
-                    umma_ss(tmem + kColV, desc_mnmajor(sA + k * 2048, kTile), desc_mnmajor(g0 + k * 2048, kTile), idV,
-                            (ii > 0 || k > 0) ? 1u : 0u);
-                umma_commit(bar(DW_TEMPTY + s));
+                    umma_ss(tmem + kColV, dAmn + k * 128, dg + k * 128, idV, (!first || k > 0) ? 1u : 0u);
+                umma_commit(bar(DW_TEMPTY + st));
                 umma_commit(bar(DW_PEMPTY));
                 return true;
             };
             bool ok = mbar_wait(bar(DW_WFULL), 0, ctl, W + 3);
+            int st = 0, st_prev = 0;
+            uint32_t ph = 0;
             for (int i = 0; ok && i < ntiles; ++i) {
-                const int s = i % L::kTokStages, n = i / L::kTokStages;
-                if (!mbar_wait(bar(DW_TFULL + s), n & 1, ctl, W + 4)) { ok = false; break; }
+                if (!mbar_wait(bar(DW_TFULL + st), ph, ctl, W + 4)) { ok = false; break; }
                 if (!mbar_wait(bar(DW_SEMPTY), (i & 1) ^ 1, ctl, W + 5)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t q0 = sTok + s * L::kTokStage, g0 = q0 + L::kChunks * kTile;
+                const uint64_t dq = dQk0 + st * kTokStep, dg = dGk0 + st * kTokStep;
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const int c = k >> 2, kk = k & 3;
-                    umma_ss(tmem + kColS, desc_kmajor(q0 + c * kTile + kk * 32),
-                            desc_kmajor(sW + c * 2 * kWChunk + kk * 32), idS, k > 0 ? 1u : 0u);
+                    umma_ss(tmem + kColS, dq + ((c * kTile + kk * 32) >> 4), dKU + ((c * 2 * kWChunk + kk * 32) >> 4), idS,
+                            k > 0 ? 1u : 0u);
                 }
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const int c = k >> 2, kk = k & 3;
-                    umma_ss(tmem + kColdA, desc_kmajor(g0 + c * kTile + kk * 32),
-                            desc_kmajor(sW + L::kOffWV + c * kWChunk + kk * 32), idA, k > 0 ? 1u : 0u);
+                    umma_ss(tmem + kColdA, dg + ((c * kTile + kk * 32) >> 4), dV + ((c * kWChunk + kk * 32) >> 4), idA,
+                            k > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(DW_SFULL));
-                if (i > 0) ok = gemm34(i - 1);
+                if (i > 0) ok = gemm34(st_prev, (i - 1) & 1, i == 1);
+                st_prev = st;
+                if (++st == L::kTokStages) { st = 0; ph ^= 1; }
             }
-            if (ok) ok = gemm34(ntiles - 1);
+            if (ok) ok = gemm34(st_prev, (ntiles - 1) & 1, ntiles == 1);
             umma_commit(bar(DW_ACCFULL));
         }
     } else if (warp >= 4) {

@@ -1,32 +1,56 @@
 // Forward kernel, bf16, sm_100a:  O = sum_e R_e * ((SiLU(Q K_e^T) * (Q U_e^T)) V_e).
 //
 // One CTA owns one tile of 128 token rows of one (batch, head).  Its Q tile is loaded once; the
-// weights of the head stream through a ring of shared-memory stages, 64 intermediate rows
-// (one "block": 64 rows of K_e, U_e and V_e) per stage.  Per block the tensor core computes
+// weights of the head stream through shared-memory rings, 64 intermediate rows (one "block": 64
+// rows of K_e, U_e and V_e) at a time.  Per block the tensor core computes
 //     S = Q [K_blk; U_blk]^T      (128 x 128, one MMA chain, fp32 in tensor memory: M | N)
-// the activation warps read S, form A = bf16(SiLU(M) * N * R_e) in registers and write it to a
-// shared-memory operand tile, and the tensor core accumulates
+// an activation warpgroup reads S, forms A = bf16(SiLU(M) * N * R_e) in registers and writes it
+// back into tensor memory over the first 32 columns of the same S buffer (two bf16 per column), and
+// the tensor core accumulates, with A read from tensor memory and V from shared memory,
 //     O += A V_blk                (128 x d_h, fp32 in tensor memory, over all blocks of all e)
-// so the [T, E*d_e] intermediate never leaves the SM.  S and A are double-buffered so the MMA of
-// block j+1 overlaps the activation of block j.
+// so the [T, E*d_e] intermediate never leaves the SM and A never touches shared memory.
 //
-// Warp roles (384 threads): warp 0 TMA producer, warp 1 MMA issuer + tensor-memory owner,
-// warps 2-3 idle, warps 4-11 activation/epilogue (warp % 4 = TMEM lane quarter = 32 token rows,
-// (warp-4)/4 = which 32 of the block's 64 intermediate columns).
+// Pipeline.  The hand-off from an MMA to the warps that consume its result costs several hundred
+// cycles (commit -> mbarrier -> wake-up) and the tensor pipe accepts MMAs only a few ahead of their
+// execution, so (a) three S buffers keep three blocks in flight, (b) the two MMA chains are issued
+// by two different threads -- one runs ahead with S = Q [K;U]^T, the other follows with O += A V --
+// so that neither waits on the other's barriers, and (c) the two activation warpgroups own
+// alternate blocks (even / odd), so the load/store phases of one overlap the arithmetic of the other.
 //
-// Tensor memory (512 columns): O at [0, d_h), S buffers at [128, 256) and [256, 384).
+// Warp roles (384 threads): warp 0 TMA producer, warps 1-2 MMA issuers for S (even / odd blocks;
+// warp 1 owns tensor memory), warp 3 MMA issuer for O, warps 4-7 activation warpgroup 0,
+// warps 8-11 activation warpgroup 1 (warp % 4 = TMEM lane quarter = 32 token rows; one thread = one
+// token row of a block).
+//
+// Tensor memory (512 columns): O at [0, d_h), S buffers at [128, 256), [256, 384), [384, 512).
 #include "kernels.h"
 #include "tc_common.cuh"
 #include "tensormap.cuh"
+
+#ifdef FMHF_TRACE
+// Debug build only: per-block clock stamps of CTA (1,0,0) for pipeline analysis.
+__device__ unsigned int g_fwd_trace[4][64][8];
+#define FMHF_TR(role, j, ev)                                                                   \
+    do {                                                                                       \
+        if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 64)                  \
+            g_fwd_trace[role][j][ev] = (unsigned int)clock64();                                 \
+    } while (0)
+extern "C" int flashmhf_debug_read_fwd_trace(unsigned int *out) {
+    return (int)cudaMemcpyFromSymbol(out, g_fwd_trace, sizeof(g_fwd_trace));
+}
+#else
+#define FMHF_TR(role, j, ev) do { } while (0)
+#endif
 
 namespace fmhf {
 namespace {
 
 constexpr int kBT = 128;  // token rows per tile
 constexpr int kBI = 64;   // intermediate rows per block
-constexpr int kStages = 3;
+constexpr int kDepth = 3; // S buffers in tensor memory = blocks in flight
+constexpr int kRing = 4;  // shared-memory stages of the [K;U] ring and of the V ring
 constexpr int kThreads = 384;
-constexpr int kActThreads = 256;
+constexpr int kGroupThreads = 128;  // one activation warpgroup
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS0 = 128, kColSStride = 128;
 
@@ -35,28 +59,37 @@ struct FwdSmem {
     static constexpr int kChunks = (DH + 63) / 64;              // 64-column SW128 chunks per row of d_h
     static constexpr uint32_t kQBytes = kChunks * kBT * 128;    // Q tile (also the O staging tile)
     static constexpr uint32_t kWChunk = kBI * 128;              // one 64-row x 64-col weight chunk
-    static constexpr uint32_t kStageBytes = 3 * kChunks * kWChunk;
-    static constexpr uint32_t kABytes = kBT * 128;              // A tile: 128 rows x 64 cols
+    static constexpr uint32_t kKUStage = 2 * kChunks * kWChunk; // per chunk: K rows then U rows = one 128-row K-major tile
+    static constexpr uint32_t kVStage = kChunks * kWChunk;
     // offsets from the 1024-aligned base
     static constexpr uint32_t kOffQ = 0;
-    static constexpr uint32_t kOffW = kOffQ + kQBytes;
-    static constexpr uint32_t kOffA = kOffW + kStages * kStageBytes;
-    static constexpr uint32_t kOffBar = kOffA + 2 * kABytes;
+    static constexpr uint32_t kOffKU = kOffQ + kQBytes;
+    static constexpr uint32_t kOffV = kOffKU + kRing * kKUStage;
+    static constexpr uint32_t kOffBar = kOffV + kRing * kVStage;
     static constexpr uint32_t kTotal = kOffBar + 256 + 1024;  // + barriers/control + alignment slack
-    // inside a stage: chunk c of K at c*2*kWChunk, of U right behind it (so [K;U] of one chunk is one
-    // 128-row K-major tile), V chunks after all K/U chunks.
-    static constexpr uint32_t kOffV = 2 * kChunks * kWChunk;
 };
 
 // barrier slots (8 bytes each) inside the control area
-enum { BAR_Q = 0, BAR_WFULL = 1, BAR_WEMPTY = 4, BAR_SFULL = 7, BAR_SEMPTY = 9, BAR_AFULL = 11, BAR_AEMPTY = 13,
-       BAR_OFULL = 15, BAR_COUNT = 16 };
+// SFULL: S computed; AFULL: A written over it; SFREE: O += A V done, buffer reusable
+enum { BAR_Q = 0, BAR_KUFULL = 1, BAR_KUEMPTY = 5, BAR_VFULL = 9, BAR_VEMPTY = 13, BAR_SFULL = 17, BAR_AFULL = 20,
+       BAR_SFREE = 23, BAR_OFULL = 26, BAR_COUNT = 27 };
 
 struct FwdArgs {
     const float *R;
     long long r_sb, r_sh, r_ss;
     int S, E, De, G;
     int *status;
+};
+
+// Ring position of block j in a ring of N slots: slot j % N and the parity of its lap.
+template <int N>
+struct RingPos {
+    int slot = 0;
+    uint32_t lap = 0;
+    __device__ __forceinline__ void advance(int by) {
+        slot += by;
+        if (slot >= N) { slot -= N; lap ^= 1; }
+    }
 };
 
 template <int DH>
@@ -69,7 +102,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *gbase = smem_raw + (base - raw);
-    const uint32_t sQ = base + L::kOffQ, sW = base + L::kOffW, sA = base + L::kOffA, sBar = base + L::kOffBar;
+    const uint32_t sQ = base + L::kOffQ, sKU = base + L::kOffKU, sV = base + L::kOffV, sBar = base + L::kOffBar;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gbase + L::kOffBar + BAR_COUNT * 8);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(gbase + L::kOffBar + BAR_COUNT * 8 + 4);
     auto bar = [&](int i) { return sBar + 8u * i; };
@@ -84,15 +117,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     if (threadIdx.x == 0) {
         *abort_flag = (*reinterpret_cast<volatile int *>(args.status) != 0);  // an earlier CTA gave up: drain fast
         mbar_init(bar(BAR_Q), 1);
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(bar(BAR_WFULL + s), 1);
-            mbar_init(bar(BAR_WEMPTY + s), 1);
+        for (int i = 0; i < kRing; ++i) {
+            mbar_init(bar(BAR_KUFULL + i), 1);
+            mbar_init(bar(BAR_KUEMPTY + i), 1);
+            mbar_init(bar(BAR_VFULL + i), 1);
+            mbar_init(bar(BAR_VEMPTY + i), 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kDepth; ++i) {
             mbar_init(bar(BAR_SFULL + i), 1);
-            mbar_init(bar(BAR_SEMPTY + i), kActThreads);
-            mbar_init(bar(BAR_AFULL + i), kActThreads);
-            mbar_init(bar(BAR_AEMPTY + i), 1);
+            mbar_init(bar(BAR_AFULL + i), kGroupThreads);
+            mbar_init(bar(BAR_SFREE + i), 1);
         }
         mbar_init(bar(BAR_OFULL), 1);
         fence_mbar_init();
@@ -115,104 +149,158 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             tma_prefetch_desc(&tmV);
             mbar_arrive_expect_tx(bar(BAR_Q), L::kQBytes);
             for (int c = 0; c < L::kChunks; ++c) tma_load_4d(sQ + c * (kBT * 128), &tmQ, bar(BAR_Q), c * 64, t0, h, b);
-            for (int j = 0; j < nblk; ++j) {
-                const int s = j % kStages, n = j / kStages;
-                if (!mbar_wait(bar(BAR_WEMPTY + s), (n & 1) ^ 1, ctl, W + 1)) break;
-                const uint32_t st = sW + s * L::kStageBytes;
-                mbar_arrive_expect_tx(bar(BAR_WFULL + s), L::kStageBytes);
-                const int row = j * kBI;
-                for (int c = 0; c < L::kChunks; ++c) {
-                    tma_load_3d(st + c * 2 * L::kWChunk, &tmK, bar(BAR_WFULL + s), c * 64, row, hk);
-                    tma_load_3d(st + c * 2 * L::kWChunk + L::kWChunk, &tmU, bar(BAR_WFULL + s), c * 64, row, hk);
+            // [K;U] of block j, then V of block j-2: V is consumed about two blocks later than K and U of
+            // the same block, so with this lag the producer never waits on the V ring while a [K;U]
+            // stage is free.
+            RingPos<kRing> pk, pv;
+            for (int j = 0; j < nblk + 2; ++j) {
+                if (j < nblk) {
+                    FMHF_TR(0, j, 0);
+                    if (!mbar_wait(bar(BAR_KUEMPTY + pk.slot), pk.lap ^ 1, ctl, W + 1)) break;
+                    FMHF_TR(0, j, 1);
+                    const uint32_t fku = bar(BAR_KUFULL + pk.slot), dku = sKU + pk.slot * L::kKUStage;
+                    mbar_arrive_expect_tx(fku, L::kKUStage);
+#pragma unroll
+                    for (int c = 0; c < L::kChunks; ++c) {
+                        tma_load_3d(dku + c * 2 * L::kWChunk, &tmK, fku, c * 64, j * kBI, hk);
+                        tma_load_3d(dku + c * 2 * L::kWChunk + L::kWChunk, &tmU, fku, c * 64, j * kBI, hk);
+                    }
+                    pk.advance(1);
                 }
-                for (int c = 0; c < L::kChunks; ++c)
-                    tma_load_3d(st + L::kOffV + c * L::kWChunk, &tmV, bar(BAR_WFULL + s), c * 64, row, hk);
+                if (j >= 2) {
+                    if (!mbar_wait(bar(BAR_VEMPTY + pv.slot), pv.lap ^ 1, ctl, W + 2)) break;
+                    const uint32_t fv = bar(BAR_VFULL + pv.slot), dv = sV + pv.slot * L::kVStage;
+                    mbar_arrive_expect_tx(fv, L::kVStage);
+#pragma unroll
+                    for (int c = 0; c < L::kChunks; ++c)
+                        tma_load_3d(dv + c * L::kWChunk, &tmV, fv, c * 64, (j - 2) * kBI, hk);
+                    pv.advance(1);
+                }
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp == 1 || warp == 2) {
+        // ------------------------------------------------------------------ MMA issuers for S = Q [K;U]^T
+        // Two threads (warp 1: even blocks, warp 2: odd blocks): while one is between batches -- barrier
+        // polls, commits -- the other keeps the tensor pipe fed.  Blocks are independent (own S buffer).
+        // One thread issues the chain, so its instruction stream is kept minimal: descriptors are built
+        // once and advanced by adding constants (the address field counts 16-byte units).
         if (lane == 0) {
-            constexpr uint32_t idesc1 = umma_idesc(128, 2 * kBI, false, false);  // S = Q [K;U]^T
-            constexpr uint32_t idesc2 = umma_idesc(128, DH, false, true);        // O += A V  (V is MN-major)
-            auto gemm2 = [&](int jj) -> bool {  // O += A(jj) V(jj)
-                const int s = jj % kStages, bb = jj & 1, nb = jj >> 1;
-                if (!mbar_wait(bar(BAR_AFULL + bb), nb & 1, ctl, W + 4)) return false;
+            constexpr uint32_t idesc1 = umma_idesc(128, 2 * kBI, false, false);
+            const uint64_t dQ = desc_kmajor(sQ), dKU0 = desc_kmajor(sKU);
+            constexpr uint64_t kKUStep = L::kKUStage >> 4;
+            const int first = warp - 1;
+            bool ok = mbar_wait(bar(BAR_Q), 0, ctl, W + 3);
+            RingPos<kRing> pw;   // [K;U] stage of block j
+            RingPos<kDepth> ps;  // S buffer of block j
+            pw.advance(first);
+            ps.advance(first);
+            for (int j = first; ok && j < nblk; j += 2) {
+                FMHF_TR(1, j, 0);
+                if (!mbar_wait(bar(BAR_KUFULL + pw.slot), pw.lap, ctl, W + 4)) break;
+                FMHF_TR(1, j, 1);
+                if (!mbar_wait(bar(BAR_SFREE + ps.slot), ps.lap ^ 1, ctl, W + 5)) break;
+                FMHF_TR(1, j, 2);
                 tc_fence_after();
-                const uint32_t a0 = sA + bb * L::kABytes, v0 = sW + s * L::kStageBytes + L::kOffV;
-#pragma unroll
-                for (int k = 0; k < kBI / 16; ++k)
-                    umma_ss(tmem + kColO, desc_kmajor(a0 + k * 32), desc_mnmajor(v0 + k * 2048, L::kWChunk), idesc2,
-                            (jj > 0 || k > 0) ? 1u : 0u);
-                umma_commit(bar(BAR_WEMPTY + s));
-                umma_commit(bar(BAR_AEMPTY + bb));
-                return true;
-            };
-            bool ok = mbar_wait(bar(BAR_Q), 0, ctl, W + 2);
-            for (int j = 0; ok && j < nblk; ++j) {
-                const int s = j % kStages, n = j / kStages, bb = j & 1, nb = j >> 1;
-                if (!mbar_wait(bar(BAR_WFULL + s), n & 1, ctl, W + 3)) { ok = false; break; }
-                if (!mbar_wait(bar(BAR_SEMPTY + bb), (nb & 1) ^ 1, ctl, W + 5)) { ok = false; break; }
-                tc_fence_after();
-                const uint32_t st = sW + s * L::kStageBytes;
+                const uint64_t dku = dKU0 + pw.slot * kKUStep;
+                const uint32_t tS = tmem + kColS0 + ps.slot * kColSStride;
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const int c = k >> 2, kk = k & 3;
-                    umma_ss(tmem + kColS0 + bb * kColSStride, desc_kmajor(sQ + c * (kBT * 128) + kk * 32),
-                            desc_kmajor(st + c * 2 * L::kWChunk + kk * 32), idesc1, k > 0 ? 1u : 0u);
+                    umma_ss(tS, dQ + ((c * (kBT * 128) + kk * 32) >> 4), dku + ((c * 2 * L::kWChunk + kk * 32) >> 4),
+                            idesc1, k > 0 ? 1u : 0u);
                 }
-                umma_commit(bar(BAR_SFULL + bb));
-                if (j > 0) ok = gemm2(j - 1);
+                umma_commit(bar(BAR_KUEMPTY + pw.slot));
+                umma_commit(bar(BAR_SFULL + ps.slot));
+                FMHF_TR(1, j, 3);
+                pw.advance(2);
+                ps.advance(2);
             }
-            if (ok) ok = gemm2(nblk - 1);
-            umma_commit(bar(BAR_OFULL));
+        }
+    } else if (warp == 3) {
+        // ------------------------------------------------------------------ MMA issuer 2: O += A V
+        // A comes from tensor memory (the first 32 columns of the block's S buffer), V from shared
+        // memory as an MN-major operand.
+        if (lane == 0) {
+            constexpr uint32_t idesc2 = umma_idesc(128, DH, false, true);
+            const uint64_t dV0 = desc_mnmajor(sV, L::kWChunk);
+            constexpr uint64_t kVStep = L::kVStage >> 4;
+            RingPos<kRing> pw;
+            RingPos<kDepth> ps;
+            bool ok = true;
+            for (int j = 0; j < nblk; ++j) {
+                if (!mbar_wait(bar(BAR_VFULL + pw.slot), pw.lap, ctl, W + 6)) { ok = false; break; }
+                if (!mbar_wait(bar(BAR_AFULL + ps.slot), ps.lap, ctl, W + 7)) { ok = false; break; }
+                FMHF_TR(1, j, 4);
+                tc_fence_after();
+                const uint64_t dv = dV0 + pw.slot * kVStep;
+                const uint32_t tA = tmem + kColS0 + ps.slot * kColSStride;
+#pragma unroll
+                for (int k = 0; k < kBI / 16; ++k)
+                    umma_ts(tmem + kColO, tA + k * 8, dv + k * 128, idesc2, (j > 0 || k > 0) ? 1u : 0u);
+                umma_commit(bar(BAR_VEMPTY + pw.slot));
+                umma_commit(bar(BAR_SFREE + ps.slot));
+                FMHF_TR(1, j, 5);
+                pw.advance(1);
+                ps.advance(1);
+            }
+            if (ok) umma_commit(bar(BAR_OFULL));
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ activation + epilogue
-        const int quarter = warp & 3, half = (warp - 4) >> 2;
+        const int quarter = warp & 3, group = (warp - 4) >> 2;  // group 0: even blocks, group 1: odd blocks
         const int row = quarter * 32 + lane;
         const int t = t0 + row;
         const bool in_range = t < args.S;
         const float *rrow = args.R + (long long)b * args.r_sb + (long long)h * args.r_sh + (long long)t * args.r_ss;
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-        float r_cur = 0.f, r_next = in_range ? __ldg(rrow) : 0.f;  // routing weight, fetched one sub-network ahead
         bool ok = true;
-        for (int j = 0; j < nblk; ++j) {
-            const int bb = j & 1, nb = j >> 1;
-            if (j % blocks_per_e == 0) {
-                const int e1 = j / blocks_per_e + 1;
-                r_cur = r_next;
-                r_next = (in_range && e1 < args.E) ? __ldg(rrow + e1) : 0.f;
-            }
-            if (!mbar_wait(bar(BAR_SFULL + bb), nb & 1, ctl, W + 6)) { ok = false; break; }
-            tc_fence_after();
-            uint32_t m[32], n[32];
-            const uint32_t ts = lane_base + kColS0 + bb * kColSStride + half * 32;
-            tmem_ld32(ts, m);
-            tmem_ld32(ts + kBI, n);
-            tmem_ld_wait();
-            tc_fence_before();
-            mbar_arrive(bar(BAR_SEMPTY + bb));
-            uint32_t a[16];
+        // sub-network of this group's current block and position inside it; routing weight fetched a block ahead
+        int e = 0, in_e = group;
+        while (in_e >= blocks_per_e) { in_e -= blocks_per_e; ++e; }
+        float r_cur = (in_range && e < args.E) ? __ldg(rrow + e) : 0.f;
+        RingPos<kDepth> p;
+        p.advance(group);
+        for (int j = group; j < nblk; j += 2) {
+            int e_nb = e, in_nb = in_e + 2;  // where this group's next block lies
+            while (in_nb >= blocks_per_e) { in_nb -= blocks_per_e; ++e_nb; }
+            const float r_nb = (e_nb != e && in_range && e_nb < args.E) ? __ldg(rrow + e_nb) : r_cur;
             const f32x2 half_r = f2_pack(0.5f * r_cur, 0.5f * r_cur);
+            FMHF_TR(2 + group, j, 0);
+            if (!mbar_wait(bar(BAR_SFULL + p.slot), p.lap, ctl, W + 8)) { ok = false; break; }
+            FMHF_TR(2 + group, j, 1);
+            tc_fence_after();
+            const uint32_t ts = lane_base + kColS0 + p.slot * kColSStride;
+            uint32_t a[32];  // 64 bf16 of this row of A
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-                a[i] = fwd_act_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]), f2_pack_bits(n[2 * i], n[2 * i + 1]), half_r);
-            if (!mbar_wait(bar(BAR_AEMPTY + bb), (nb & 1) ^ 1, ctl, W + 7)) { ok = false; break; }
-            const uint32_t arow = sA + bb * L::kABytes;
+            for (int part = 0; part < 2; ++part) {
+                uint32_t m[32], n[32];
+                tmem_ld32(ts + part * 32, m);
+                tmem_ld32(ts + kBI + part * 32, n);
+                tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-                st_shared_v4(arow + sw128_offset(row, half * 4 + i), a[4 * i], a[4 * i + 1], a[4 * i + 2], a[4 * i + 3]);
-            fence_async_smem();
-            mbar_arrive(bar(BAR_AFULL + bb));
+                for (int i = 0; i < 16; ++i)
+                    a[part * 16 + i] = fwd_act_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]),
+                                                    f2_pack_bits(n[2 * i], n[2 * i + 1]), half_r);
+            }
+            FMHF_TR(2 + group, j, 3);
+            tmem_st32(ts, a);  // over M[0:32] of this buffer, which is in registers by now
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(bar(BAR_AFULL + p.slot));
+            FMHF_TR(2 + group, j, 5);
+            p.advance(2);
+            r_cur = r_nb;
+            e = e_nb;
+            in_e = in_nb;
         }
         // epilogue: O (fp32, tensor memory) -> bf16 -> shared (over the Q tile) -> TMA store
-        if (ok) ok = mbar_wait(bar(BAR_OFULL), 0, ctl, W + 8);
+        if (ok) ok = mbar_wait(bar(BAR_OFULL), 0, ctl, W + 10);
         if (ok) {
             tc_fence_after();
-            constexpr int kColsPerHalf = DH / 2;  // 64, 48 or 32 columns per thread
-            const int c0 = half * kColsPerHalf;
+            constexpr int kColsPerGroup = DH / 2;  // 64, 48 or 32 columns per thread
+            const int c0 = group * kColsPerGroup;
 #pragma unroll
-            for (int g = 0; g < kColsPerHalf / 16; ++g) {
+            for (int g = 0; g < kColsPerGroup / 16; ++g) {
                 uint32_t o[16];
                 tmem_ld16(lane_base + kColO + c0 + g * 16, o);
                 tmem_ld_wait();
@@ -229,7 +317,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             tc_fence_before();
             fence_async_smem();
         }
-        named_bar_sync(1, kActThreads);
+        named_bar_sync(1, 2 * kGroupThreads);
         if (ok && warp == 4 && lane == 0 && !*abort_flag) {
             for (int c = 0; c < L::kChunks; ++c) tma_store_4d(&tmO, sQ + c * (kBT * 128), c * 64, t0, h, b);
             tma_store_commit();
