@@ -448,37 +448,22 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
         }
     } else if (warp == 1) {
-        // One thread issues every MMA: descriptors are built once and advanced by constants.
+        // MMA issuer 1: the recompute chain S = Q [K;U]^T, dA = dO V^T of each token tile.  The two
+        // chains have their own issuing threads so that neither waits on the other's barriers and the
+        // tensor pipe, which accepts MMAs only a few ahead of execution, is fed by whichever is ready.
+        // Descriptors are built once and advanced by constants (16-byte units).
         if (lane == 0) {
-            constexpr uint32_t idS = umma_idesc(128, 2 * kBI, false, false);  // S  = Q  [K;U]^T
-            constexpr uint32_t idA = umma_idesc(128, kBI, false, false);      // dA = dO V^T
-            constexpr uint32_t idKU = umma_idesc(128, DH, true, true);        // [dK;dU] += [dM|dN]^T Q
-            constexpr uint32_t idV = umma_idesc(64, DH, true, true);          // dV      += A^T dO
+            constexpr uint32_t idS = umma_idesc(128, 2 * kBI, false, false);
+            constexpr uint32_t idA = umma_idesc(128, kBI, false, false);
             const uint64_t dQk0 = desc_kmajor(sTok), dGk0 = desc_kmajor(sTok + L::kChunks * kTile),
-                           dQmn0 = desc_mnmajor(sTok, kTile), dGmn0 = desc_mnmajor(sTok + L::kChunks * kTile, kTile),
-                           dKU = desc_kmajor(sW), dV = desc_kmajor(sW + L::kOffWV), dPmn = desc_mnmajor(sP, kTile),
-                           dAmn = desc_mnmajor(sA, kTile);
+                           dKU = desc_kmajor(sW), dV = desc_kmajor(sW + L::kOffWV);
             constexpr uint64_t kTokStep = L::kTokStage >> 4;
-            auto gemm34 = [&](int st, uint32_t p_parity, bool first) -> bool {
-                if (!mbar_wait(bar(DW_PFULL), p_parity, ctl, W + 6)) return false;
-                tc_fence_after();
-                const uint64_t dq = dQmn0 + st * kTokStep, dg = dGmn0 + st * kTokStep;
-#pragma unroll
-                for (int k = 0; k < kBT / 16; ++k)
-                    umma_ss(tmem + kColKU, dPmn + k * 128, dq + k * 128, idKU, (!first || k > 0) ? 1u : 0u);
-#pragma unroll
-                for (int k = 0; k < kBT / 16; ++k)
-                    umma_ss(tmem + kColV, dAmn + k * 128, dg + k * 128, idV, (!first || k > 0) ? 1u : 0u);
-                umma_commit(bar(DW_TEMPTY + st));
-                umma_commit(bar(DW_PEMPTY));
-                return true;
-            };
             bool ok = mbar_wait(bar(DW_WFULL), 0, ctl, W + 3);
-            int st = 0, st_prev = 0;
+            int st = 0;
             uint32_t ph = 0;
             for (int i = 0; ok && i < ntiles; ++i) {
-                if (!mbar_wait(bar(DW_TFULL + st), ph, ctl, W + 4)) { ok = false; break; }
-                if (!mbar_wait(bar(DW_SEMPTY), (i & 1) ^ 1, ctl, W + 5)) { ok = false; break; }
+                if (!mbar_wait(bar(DW_TFULL + st), ph, ctl, W + 4)) break;
+                if (!mbar_wait(bar(DW_SEMPTY), (i & 1) ^ 1, ctl, W + 5)) break;
                 tc_fence_after();
                 const uint64_t dq = dQk0 + st * kTokStep, dg = dGk0 + st * kTokStep;
 #pragma unroll
@@ -494,12 +479,34 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                             k > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(DW_SFULL));
-                if (i > 0) ok = gemm34(st_prev, (i - 1) & 1, i == 1);
-                st_prev = st;
                 if (++st == L::kTokStages) { st = 0; ph ^= 1; }
             }
-            if (ok) ok = gemm34(st_prev, (ntiles - 1) & 1, ntiles == 1);
-            umma_commit(bar(DW_ACCFULL));
+        }
+    } else if (warp == 3) {
+        // MMA issuer 2: the accumulation chain [dK;dU] += [dM|dN]^T Q, dV += A^T dO.
+        if (lane == 0) {
+            constexpr uint32_t idKU = umma_idesc(128, DH, true, true);
+            constexpr uint32_t idV = umma_idesc(64, DH, true, true);
+            const uint64_t dQmn0 = desc_mnmajor(sTok, kTile), dGmn0 = desc_mnmajor(sTok + L::kChunks * kTile, kTile),
+                           dPmn = desc_mnmajor(sP, kTile), dAmn = desc_mnmajor(sA, kTile);
+            constexpr uint64_t kTokStep = L::kTokStage >> 4;
+            int st = 0;
+            bool ok = true;
+            for (int i = 0; i < ntiles; ++i) {
+                if (!mbar_wait(bar(DW_PFULL), i & 1, ctl, W + 6)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t dq = dQmn0 + st * kTokStep, dg = dGmn0 + st * kTokStep;
+#pragma unroll
+                for (int k = 0; k < kBT / 16; ++k)
+                    umma_ss(tmem + kColKU, dPmn + k * 128, dq + k * 128, idKU, (i > 0 || k > 0) ? 1u : 0u);
+#pragma unroll
+                for (int k = 0; k < kBT / 16; ++k)
+                    umma_ss(tmem + kColV, dAmn + k * 128, dg + k * 128, idV, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(bar(DW_TEMPTY + st));
+                umma_commit(bar(DW_PEMPTY));
+                if (++st == L::kTokStages) st = 0;
+            }
+            if (ok) umma_commit(bar(DW_ACCFULL));
         }
     } else if (warp >= 4) {
         const int quarter = warp & 3, half = (warp - 4) >> 2;
