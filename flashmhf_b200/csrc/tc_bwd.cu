@@ -18,8 +18,8 @@
 //   Each CTA writes fp32 partial sums to the workspace; dw_reduce_kernel adds the splits in a fixed
 //   order and writes bf16 dK, dU, dV.
 //
-// Both use 384 threads: warp 0 TMA producer, warp 1 MMA issuer and tensor-memory owner, warps 4-11
-// element-wise math (warp % 4 = TMEM lane quarter, (warp-4)/4 = which 32 of the 64 block columns).
+// Both use 384 threads: warp 0 TMA producer, warps 1 and 3 MMA issuers (one per MMA chain; warp 1 owns
+// tensor memory), warps 4-11 element-wise math (warp % 4 = TMEM lane quarter, (warp-4)/4 = which 32 of the 64 block columns).
 #include <mutex>
 
 #include "kernels.h"
@@ -171,35 +171,24 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
         }
     } else if (warp == 1) {
-        // One thread issues every MMA: descriptors are built once and advanced by constants.
+        // MMA issuer 1: the recompute chain S = Q [K;U]^T, dA = dO V^T.  The two chains have their own
+        // issuing threads so that neither waits on the other's barriers and the tensor pipe, which
+        // accepts MMAs only a few ahead of execution, is fed by whichever is ready.  Descriptors are
+        // built once and advanced by constants (16-byte units).
         if (lane == 0) {
-            constexpr uint32_t idS = umma_idesc(128, 2 * kBI, false, false);  // S  = Q  [K;U]^T
-            constexpr uint32_t idA = umma_idesc(128, kBI, false, false);      // dA = dO V^T
-            constexpr uint32_t idQ = umma_idesc(128, DH, false, true);        // dQ += [dM|dN] [K;U]
-            const uint64_t dQd = desc_kmajor(sQ), dOd = desc_kmajor(sdO), dKU0 = desc_kmajor(sKU), dV0 = desc_kmajor(sV),
-                           dP = desc_kmajor(sP), dKUmn0 = desc_mnmajor(sKU, 2 * kWChunk);
+            constexpr uint32_t idS = umma_idesc(128, 2 * kBI, false, false);
+            constexpr uint32_t idA = umma_idesc(128, kBI, false, false);
+            const uint64_t dQd = desc_kmajor(sQ), dOd = desc_kmajor(sdO), dKU0 = desc_kmajor(sKU), dV0 = desc_kmajor(sV);
             constexpr uint64_t kKUStep = L::kKUStage >> 4, kVStep = L::kVStage >> 4;
-            auto gemm3 = [&](int sk, uint32_t p_parity, bool first) -> bool {
-                if (!mbar_wait(bar(DQ_PFULL), p_parity, ctl, W + 6)) return false;
-                tc_fence_after();
-                const uint64_t dku = dKUmn0 + sk * kKUStep;
-#pragma unroll
-                for (int k = 0; k < 8; ++k)  // K = 128: 64 columns of dM (rows of K) then 64 of dN (rows of U)
-                    umma_ss(tmem + kColAcc, dP + (((k >> 2) * kTile + (k & 3) * 32) >> 4), dku + k * 128, idQ,
-                            (!first || k > 0) ? 1u : 0u);
-                umma_commit(bar(DQ_KUEMPTY + sk));
-                umma_commit(bar(DQ_PEMPTY));
-                return true;
-            };
             bool ok = mbar_wait(bar(DQ_QFULL), 0, ctl, W + 3);
-            int sk = 0, sv = 0, sk_prev = 0;
+            int sk = 0, sv = 0;
             uint32_t phk = 0, phv = 0;
             for (int j = 0; ok && j < nblk; ++j) {
                 const int bb = j & 1;
                 const uint32_t ph_b = (j >> 1) & 1;
-                if (!mbar_wait(bar(DQ_KUFULL + sk), phk, ctl, W + 4)) { ok = false; break; }
-                if (!mbar_wait(bar(DQ_VFULL + sv), phv, ctl, W + 4)) { ok = false; break; }
-                if (!mbar_wait(bar(DQ_SEMPTY + bb), ph_b ^ 1, ctl, W + 5)) { ok = false; break; }
+                if (!mbar_wait(bar(DQ_KUFULL + sk), phk, ctl, W + 4)) break;
+                if (!mbar_wait(bar(DQ_VFULL + sv), phv, ctl, W + 4)) break;
+                if (!mbar_wait(bar(DQ_SEMPTY + bb), ph_b ^ 1, ctl, W + 5)) break;
                 tc_fence_after();
                 const uint64_t dku = dKU0 + sk * kKUStep, dv = dV0 + sv * kVStep;
                 const uint32_t tS = tmem + kColS0 + bb * kBufStride;
@@ -217,13 +206,31 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 }
                 umma_commit(bar(DQ_VEMPTY + sv));
                 umma_commit(bar(DQ_SFULL + bb));
-                if (j > 0) ok = gemm3(sk_prev, (j - 1) & 1, j == 1);
-                sk_prev = sk;
                 if (++sk == L::kKUStages) { sk = 0; phk ^= 1; }
                 if (++sv == L::kVStages) { sv = 0; phv ^= 1; }
             }
-            if (ok) ok = gemm3(sk_prev, (nblk - 1) & 1, nblk == 1);
-            umma_commit(bar(DQ_ACCFULL));
+        }
+    } else if (warp == 3) {
+        // MMA issuer 2: the accumulation chain dQ += [dM|dN] [K;U].
+        if (lane == 0) {
+            constexpr uint32_t idQ = umma_idesc(128, DH, false, true);
+            const uint64_t dP = desc_kmajor(sP), dKUmn0 = desc_mnmajor(sKU, 2 * kWChunk);
+            constexpr uint64_t kKUStep = L::kKUStage >> 4;
+            int sk = 0;
+            bool ok = true;
+            for (int j = 0; j < nblk; ++j) {
+                if (!mbar_wait(bar(DQ_PFULL), j & 1, ctl, W + 6)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t dku = dKUmn0 + sk * kKUStep;
+#pragma unroll
+                for (int k = 0; k < 8; ++k)  // K = 128: 64 columns of dM (rows of K) then 64 of dN (rows of U)
+                    umma_ss(tmem + kColAcc, dP + (((k >> 2) * kTile + (k & 3) * 32) >> 4), dku + k * 128, idQ,
+                            (j > 0 || k > 0) ? 1u : 0u);
+                umma_commit(bar(DQ_KUEMPTY + sk));
+                umma_commit(bar(DQ_PEMPTY));
+                if (++sk == L::kKUStages) sk = 0;
+            }
+            if (ok) umma_commit(bar(DQ_ACCFULL));
         }
     } else if (warp >= 4) {
         const int quarter = warp & 3, half = (warp - 4) >> 2;
@@ -251,10 +258,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
                 uint32_t m[16], n[16], da[16];
-                tmem_ld16(tS + sub * 16, m);
-                tmem_ld16(tS + kBI + sub * 16, n);
-                tmem_ld16(tS + kColdA + sub * 16, da);
-                tmem_ld_wait();
+                tmem_ld16x3_sync(tS + sub * 16, tS + kBI + sub * 16, tS + kColdA + sub * 16, m, n, da);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const BwdPair x = bwd_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]), f2_pack_bits(n[2 * i], n[2 * i + 1]),
@@ -299,8 +303,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
             for (int g = 0; g < kColsPerHalf / 16; ++g) {
                 uint32_t o[16];
-                tmem_ld16(lane_base + kColAcc + c0 + g * 16, o);
-                tmem_ld_wait();
+                tmem_ld16_sync(lane_base + kColAcc + c0 + g * 16, o);
 #pragma unroll
                 for (int v = 0; v < 2; ++v) {
                     const int col = c0 + g * 16 + v * 8;
@@ -538,10 +541,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             for (int sub = 0; sub < 2; ++sub) {
                 uint32_t m[16], n[16], da[16];
                 const uint32_t c = half * 32 + sub * 16;
-                tmem_ld16(lane_base + kColS + c, m);
-                tmem_ld16(lane_base + kColS + kBI + c, n);
-                tmem_ld16(lane_base + kColdA + c, da);
-                tmem_ld_wait();
+                tmem_ld16x3_sync(lane_base + kColS + c, lane_base + kColS + kBI + c, lane_base + kColdA + c, m, n, da);
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                     const BwdPair x = bwd_pair(f2_pack_bits(m[2 * q], m[2 * q + 1]), f2_pack_bits(n[2 * q], n[2 * q + 1]),
@@ -578,8 +578,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
                 for (int g = 0; g < kColsPerHalf / 16; ++g) {
                     uint32_t o[16];
-                    tmem_ld16(lane_base + kColKU + c0 + g * 16, o);
-                    tmem_ld_wait();
+                    tmem_ld16_sync(lane_base + kColKU + c0 + g * 16, o);
 #pragma unroll
                     for (int v = 0; v < 4; ++v)
                         *reinterpret_cast<float4 *>(dst + g * 16 + v * 4) =
@@ -592,8 +591,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
                 for (int g = 0; g < kColsPerHalf / 16; ++g) {
                     uint32_t o[16];
-                    tmem_ld16(lane_base + kColV + c0 + g * 16, o);
-                    tmem_ld_wait();
+                    tmem_ld16_sync(lane_base + kColV + c0 + g * 16, o);
                     if (lane < 16) {
 #pragma unroll
                         for (int v = 0; v < 4; ++v)

@@ -274,9 +274,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 #pragma unroll
             for (int part = 0; part < 2; ++part) {
                 uint32_t m[32], n[32];
-                tmem_ld32(ts + part * 32, m);
-                tmem_ld32(ts + kBI + part * 32, n);
-                tmem_ld_wait();
+                tmem_ld32x2_sync(ts + part * 32, ts + kBI + part * 32, m, n);
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
                     a[part * 16 + i] = fwd_act_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]),
@@ -302,8 +300,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 #pragma unroll
             for (int g = 0; g < kColsPerGroup / 16; ++g) {
                 uint32_t o[16];
-                tmem_ld16(lane_base + kColO + c0 + g * 16, o);
-                tmem_ld_wait();
+                tmem_ld16_sync(lane_base + kColO + c0 + g * 16, o);
 #pragma unroll
                 for (int v = 0; v < 2; ++v) {
                     const int col = c0 + g * 16 + v * 8;  // first of 8 columns -> one 16-byte chunk
