@@ -166,7 +166,7 @@ def main():
         args.warmup = 3 if not args.small else args.warmup
 
     import flashmhf_b200 as fm
-    from flashmhf_b200 import _lib
+    from flashmhf_b200 import _lib, dp
     _lib.load()  # fails loudly if the CUDA library is missing
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -190,9 +190,7 @@ def main():
     def device_step():
         O = fm.forward_raw(Q, K, U, V, R)
         dQ, dK, dU, dV, dR = fm.backward_raw(Q, K, U, V, R, dO)
-        if dist is not None:
-            flat = torch.cat([dK.view(-1), dU.view(-1), dV.view(-1)])
-            dist.all_reduce(flat)
+        dp.allreduce_weight_grads([dK, dU, dV])  # one bucketed NCCL all-reduce; no-op on one GPU
         return O, dQ, dR
 
     def sync_all():
@@ -233,8 +231,7 @@ def main():
         k, u, v = (t.detach().requires_grad_(True) for t in (K, U, V))
         o = fm.flash_mhf(q, k, u, v, r)
         o.backward(go)
-        if dist is not None:
-            dist.all_reduce(torch.cat([k.grad.view(-1), u.grad.view(-1), v.grad.view(-1)]))
+        dp.allreduce_weight_grads([k.grad, u.grad, v.grad])
         res = (o.detach(), q.grad, r.grad, k.grad, u.grad, v.grad)
         if outs_host is None:
             outs_host = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in res]
@@ -256,10 +253,7 @@ def main():
     h2d = sum(t.numel() * t.element_size() for t in (hQ, hdO, hR))
     d2h = sum(t.numel() * t.element_size() for t in outs_host)
 
-    t_ms = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
-    if dist is not None:
-        dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
-    ms, e2e_ms = (float(x) for x in t_ms.cpu())
+    ms, e2e_ms = dp.max_over_ranks(ms, dev), dp.max_over_ranks(e2e_ms, dev)
     fl = alg_flops(B, S, H, Dh, E, De) * world
     value = fl / (ms * 1e-3) / 1e12
     e2e_value = fl / (e2e_ms * 1e-3) / 1e12
