@@ -8,7 +8,8 @@
 //
 // bwd_dq_kernel  -- token-stationary.  One CTA owns 128 token rows of one (batch, head): Q and dO
 //   tiles stay in shared memory, the head's weights stream through (K/U ring of 3, V ring of 2).
-//   Tensor memory: dQ accumulator + two buffers of {S = [M|N] (128 cols), dA (64 cols)}.
+//   Tensor memory: dQ accumulator + two buffers of {S = [M|N] (128 cols), dA (64 cols)}; the bf16
+//   [dM|dN] operand of the dQ update is written back over the dA columns and read from there.
 //   Produces dQ (TMA store) and dR (direct stores).
 //
 // bwd_dw_kernel  -- weight-stationary.  One CTA owns one 64-row block of K, U and V of one K/U/V
@@ -25,6 +26,21 @@
 #include "kernels.h"
 #include "tc_common.cuh"
 #include "tensormap.cuh"
+
+#ifdef FMHF_TRACE
+// Debug build only: per-tile clock stamps of one dK/dU/dV CTA for pipeline analysis.
+__device__ unsigned int g_dw_trace[4][64][8];
+#define FMHF_TRW(role, i, ev)                                                                  \
+    do {                                                                                       \
+        if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0 && (i) < 64)                  \
+            g_dw_trace[role][i][ev] = (unsigned int)clock64();                                  \
+    } while (0)
+extern "C" int flashmhf_debug_read_dw_trace(unsigned int *out) {
+    return (int)cudaMemcpyFromSymbol(out, g_dw_trace, sizeof(g_dw_trace));
+}
+#else
+#define FMHF_TRW(role, i, ev) do { } while (0)
+#endif
 
 namespace fmhf {
 namespace {
@@ -79,7 +95,7 @@ struct DqSmem {
 };
 
 enum { DQ_QFULL = 0, DQ_KUFULL = 1, DQ_KUEMPTY = 4, DQ_VFULL = 7, DQ_VEMPTY = 9, DQ_SFULL = 11, DQ_SEMPTY = 13,
-       DQ_PFULL = 15, DQ_PEMPTY = 16, DQ_ACCFULL = 17, DQ_DRFULL = 18, DQ_BARS = 20 };
+       DQ_PFULL = 15, DQ_ACCFULL = 17, DQ_DRFULL = 18, DQ_DAFREE = 20, DQ_BARS = 22 };
 
 struct DqArgs {
     const float *R;
@@ -120,12 +136,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         for (int s = 0; s < L::kKUStages; ++s) { mbar_init(bar(DQ_KUFULL + s), 1); mbar_init(bar(DQ_KUEMPTY + s), 1); }
         for (int s = 0; s < L::kVStages; ++s) { mbar_init(bar(DQ_VFULL + s), 1); mbar_init(bar(DQ_VEMPTY + s), 1); }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(bar(DQ_SFULL + i), 1);
-            mbar_init(bar(DQ_SEMPTY + i), kActThreads);
+            mbar_init(bar(DQ_SFULL + i), 2);             // one commit from each of the two recompute issuers
+            mbar_init(bar(DQ_SEMPTY + i), kActThreads);  // S and dA of the buffer are in registers
+            mbar_init(bar(DQ_PFULL + i), kActThreads);   // [dM|dN] written over the dA columns
+            mbar_init(bar(DQ_DAFREE + i), 1);            // the dQ update that read [dM|dN] is done
             mbar_init(bar(DQ_DRFULL + i), kActThreads / 2);
         }
-        mbar_init(bar(DQ_PFULL), kActThreads);
-        mbar_init(bar(DQ_PEMPTY), 1);
         mbar_init(bar(DQ_ACCFULL), 1);
         fence_mbar_init();
     }
@@ -171,26 +187,24 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
         }
     } else if (warp == 1) {
-        // MMA issuer 1: the recompute chain S = Q [K;U]^T, dA = dO V^T.  The two chains have their own
-        // issuing threads so that neither waits on the other's barriers and the tensor pipe, which
-        // accepts MMAs only a few ahead of execution, is fed by whichever is ready.  Descriptors are
-        // built once and advanced by constants (16-byte units).
+        // Three MMA chains, three issuing threads (warps 1, 2, 3), so that none waits on another's
+        // barriers and the tensor pipe, which accepts MMAs only a few ahead of execution, is fed by
+        // whichever is ready.  Descriptors are built once and advanced by constants (16-byte units).
+        // Issuer 1: S = Q [K;U]^T.  Its buffer is free again as soon as the element-wise warps have
+        // read it, so this chain runs well ahead.
         if (lane == 0) {
             constexpr uint32_t idS = umma_idesc(128, 2 * kBI, false, false);
-            constexpr uint32_t idA = umma_idesc(128, kBI, false, false);
-            const uint64_t dQd = desc_kmajor(sQ), dOd = desc_kmajor(sdO), dKU0 = desc_kmajor(sKU), dV0 = desc_kmajor(sV);
-            constexpr uint64_t kKUStep = L::kKUStage >> 4, kVStep = L::kVStage >> 4;
+            const uint64_t dQd = desc_kmajor(sQ), dKU0 = desc_kmajor(sKU);
+            constexpr uint64_t kKUStep = L::kKUStage >> 4;
             bool ok = mbar_wait(bar(DQ_QFULL), 0, ctl, W + 3);
-            int sk = 0, sv = 0;
-            uint32_t phk = 0, phv = 0;
+            int sk = 0;
+            uint32_t phk = 0;
             for (int j = 0; ok && j < nblk; ++j) {
                 const int bb = j & 1;
-                const uint32_t ph_b = (j >> 1) & 1;
                 if (!mbar_wait(bar(DQ_KUFULL + sk), phk, ctl, W + 4)) break;
-                if (!mbar_wait(bar(DQ_VFULL + sv), phv, ctl, W + 4)) break;
-                if (!mbar_wait(bar(DQ_SEMPTY + bb), ph_b ^ 1, ctl, W + 5)) break;
+                if (!mbar_wait(bar(DQ_SEMPTY + bb), ((j >> 1) & 1) ^ 1, ctl, W + 5)) break;
                 tc_fence_after();
-                const uint64_t dku = dKU0 + sk * kKUStep, dv = dV0 + sv * kVStep;
+                const uint64_t dku = dKU0 + sk * kKUStep;
                 const uint32_t tS = tmem + kColS0 + bb * kBufStride;
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
@@ -198,36 +212,63 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     umma_ss(tS, dQd + ((c * kTile + kk * 32) >> 4), dku + ((c * 2 * kWChunk + kk * 32) >> 4), idS,
                             k > 0 ? 1u : 0u);
                 }
+                umma_commit(bar(DQ_SFULL + bb));
+                if (++sk == L::kKUStages) { sk = 0; phk ^= 1; }
+            }
+        }
+    } else if (warp == 2) {
+        // Issuer 2: dA = dO V^T.  The dA columns are reused for [dM|dN], so they are free only after the
+        // dQ update of the block that used them last.
+        if (lane == 0) {
+            constexpr uint32_t idA = umma_idesc(128, kBI, false, false);
+            const uint64_t dOd = desc_kmajor(sdO), dV0 = desc_kmajor(sV);
+            constexpr uint64_t kVStep = L::kVStage >> 4;
+            bool ok = mbar_wait(bar(DQ_QFULL), 0, ctl, W + 3);
+            int sv = 0;
+            uint32_t phv = 0;
+            for (int j = 0; ok && j < nblk; ++j) {
+                const int bb = j & 1;
+                if (!mbar_wait(bar(DQ_VFULL + sv), phv, ctl, W + 4)) break;
+                if (!mbar_wait(bar(DQ_DAFREE + bb), ((j >> 1) & 1) ^ 1, ctl, W + 5)) break;
+                tc_fence_after();
+                const uint64_t dv = dV0 + sv * kVStep;
+                const uint32_t tA = tmem + kColS0 + bb * kBufStride + kColdA;
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const int c = k >> 2, kk = k & 3;
-                    umma_ss(tS + kColdA, dOd + ((c * kTile + kk * 32) >> 4), dv + ((c * kWChunk + kk * 32) >> 4), idA,
+                    umma_ss(tA, dOd + ((c * kTile + kk * 32) >> 4), dv + ((c * kWChunk + kk * 32) >> 4), idA,
                             k > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(DQ_VEMPTY + sv));
                 umma_commit(bar(DQ_SFULL + bb));
-                if (++sk == L::kKUStages) { sk = 0; phk ^= 1; }
                 if (++sv == L::kVStages) { sv = 0; phv ^= 1; }
             }
         }
     } else if (warp == 3) {
-        // MMA issuer 2: the accumulation chain dQ += [dM|dN] [K;U].
+        // Issuer 3: dQ += [dM|dN] [K;U], with [dM|dN] read from tensor memory.
         if (lane == 0) {
             constexpr uint32_t idQ = umma_idesc(128, DH, false, true);
-            const uint64_t dP = desc_kmajor(sP), dKUmn0 = desc_mnmajor(sKU, 2 * kWChunk);
+            const uint64_t dKUmn0 = desc_mnmajor(sKU, 2 * kWChunk);
             constexpr uint64_t kKUStep = L::kKUStage >> 4;
             int sk = 0;
             bool ok = true;
             for (int j = 0; j < nblk; ++j) {
-                if (!mbar_wait(bar(DQ_PFULL), j & 1, ctl, W + 6)) { ok = false; break; }
+                const int bb = j & 1;
+                if (!mbar_wait(bar(DQ_PFULL + bb), (j >> 1) & 1, ctl, W + 6)) { ok = false; break; }
                 tc_fence_after();
                 const uint64_t dku = dKUmn0 + sk * kKUStep;
+                const uint32_t tP = tmem + kColS0 + bb * kBufStride + kColdA;
+                // [dM|dN] sits over the 64 dA columns as packed bf16 pairs.  The thread that handled columns
+                // [32h, 32h+32) of the block wrote its dM to dA columns [32h, 32h+16) and its dN to
+                // [32h+16, 32h+32) -- columns only it had read.  K step k (16 values = 8 columns; steps 0-3
+                // pair with the K rows of the stage, 4-7 with the U rows) is at
+                // ((k%4)/2)*32 + (k/4)*16 + (k%2)*8.
 #pragma unroll
-                for (int k = 0; k < 8; ++k)  // K = 128: 64 columns of dM (rows of K) then 64 of dN (rows of U)
-                    umma_ss(tmem + kColAcc, dP + (((k >> 2) * kTile + (k & 3) * 32) >> 4), dku + k * 128, idQ,
+                for (int k = 0; k < 8; ++k)
+                    umma_ts(tmem + kColAcc, tP + ((k & 3) >> 1) * 32 + (k >> 2) * 16 + (k & 1) * 8, dku + k * 128, idQ,
                             (j > 0 || k > 0) ? 1u : 0u);
                 umma_commit(bar(DQ_KUEMPTY + sk));
-                umma_commit(bar(DQ_PEMPTY));
+                umma_commit(bar(DQ_DAFREE + bb));
                 if (++sk == L::kKUStages) sk = 0;
             }
             if (ok) umma_commit(bar(DQ_ACCFULL));
@@ -269,16 +310,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 }
             }
             tc_fence_before();
-            mbar_arrive(bar(DQ_SEMPTY + bb));
-            if (!mbar_wait(bar(DQ_PEMPTY), (j & 1) ^ 1, ctl, W + 8)) { ok = false; break; }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t off = sw128_offset(row, half * 4 + i);
-                st_shared_v4(sP + off, pm[4 * i], pm[4 * i + 1], pm[4 * i + 2], pm[4 * i + 3]);
-                st_shared_v4(sP + kTile + off, pn[4 * i], pn[4 * i + 1], pn[4 * i + 2], pn[4 * i + 3]);
-            }
-            fence_async_smem();
-            mbar_arrive(bar(DQ_PFULL));
+            mbar_arrive(bar(DQ_SEMPTY + bb));  // S may be recomputed for block j+2 from here on
+            // dM and dN go back into tensor memory as packed bf16 pairs, over the 32 dA columns this
+            // thread has just read (no other thread reads those columns)
+            tmem_st16(tS + kColdA, pm);
+            tmem_st16(tS + kColdA + 16, pn);
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(bar(DQ_PFULL + bb));
             if (++in_e == bpe) {  // sub-network finished: add the two column halves of dR_e
                 const int xb = e & 1;
                 float dr_lo, dr_hi;
@@ -438,7 +477,9 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             for (int i = 0; i < ntiles; ++i) {
                 int ts, hh, bb;
                 tile_coords(i, ts, hh, bb);
+                FMHF_TRW(0, i, 0);
                 if (!mbar_wait(bar(DW_TEMPTY + st), ph, ctl, W + 1)) break;
+                FMHF_TRW(0, i, 1);
                 const uint32_t fb = bar(DW_TFULL + st);
                 mbar_arrive_expect_tx(fb, L::kTokStage);
                 const uint32_t d = sTok + st * L::kTokStage;
@@ -465,8 +506,11 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             int st = 0;
             uint32_t ph = 0;
             for (int i = 0; ok && i < ntiles; ++i) {
+                FMHF_TRW(1, i, 0);
                 if (!mbar_wait(bar(DW_TFULL + st), ph, ctl, W + 4)) break;
+                FMHF_TRW(1, i, 1);
                 if (!mbar_wait(bar(DW_SEMPTY), (i & 1) ^ 1, ctl, W + 5)) break;
+                FMHF_TRW(1, i, 2);
                 tc_fence_after();
                 const uint64_t dq = dQk0 + st * kTokStep, dg = dGk0 + st * kTokStep;
 #pragma unroll
@@ -482,6 +526,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                             k > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(DW_SFULL));
+                FMHF_TRW(1, i, 3);
                 if (++st == L::kTokStages) { st = 0; ph ^= 1; }
             }
         }
@@ -496,7 +541,9 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             int st = 0;
             bool ok = true;
             for (int i = 0; i < ntiles; ++i) {
+                FMHF_TRW(1, i, 4);
                 if (!mbar_wait(bar(DW_PFULL), i & 1, ctl, W + 6)) { ok = false; break; }
+                FMHF_TRW(1, i, 5);
                 tc_fence_after();
                 const uint64_t dq = dQmn0 + st * kTokStep, dg = dGmn0 + st * kTokStep;
 #pragma unroll
@@ -507,6 +554,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     umma_ss(tmem + kColV, dAmn + k * 128, dg + k * 128, idV, (i > 0 || k > 0) ? 1u : 0u);
                 umma_commit(bar(DW_TEMPTY + st));
                 umma_commit(bar(DW_PEMPTY));
+                FMHF_TRW(1, i, 6);
                 if (++st == L::kTokStages) st = 0;
             }
             if (ok) umma_commit(bar(DW_ACCFULL));
@@ -533,7 +581,9 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 r_next = (t < args.S) ? __ldg(args.R + (long long)bb * args.r_sb + (long long)hh * args.r_sh +
                                               (long long)t * args.r_ss + e) : 0.f;
             }
+            FMHF_TRW(2 + half, i, 0);
             if (!mbar_wait(bar(DW_SFULL), i & 1, ctl, W + 7)) { ok = false; break; }
+            FMHF_TRW(2 + half, i, 1);
             tc_fence_after();
             uint32_t pm[16], pn[16], pa[16];
             const f32x2 r2 = f2_pack(r, r);
@@ -553,7 +603,9 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
             tc_fence_before();
             mbar_arrive(bar(DW_SEMPTY));
+            FMHF_TRW(2 + half, i, 2);
             if (!mbar_wait(bar(DW_PEMPTY), (i & 1) ^ 1, ctl, W + 8)) { ok = false; break; }
+            FMHF_TRW(2 + half, i, 3);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const uint32_t off = sw128_offset(row, half * 4 + q);
@@ -563,6 +615,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
             fence_async_smem();
             mbar_arrive(bar(DW_PFULL));
+            FMHF_TRW(2 + half, i, 4);
         }
         if (ok) ok = mbar_wait(bar(DW_ACCFULL), 0, ctl, W + 9);
         if (ok) {
