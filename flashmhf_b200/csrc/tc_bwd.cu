@@ -395,8 +395,11 @@ struct DwSmem {
     static constexpr uint32_t kTotal = kOffCtl + 256 + 1024;
 };
 
-enum { DW_WFULL = 0, DW_TFULL = 1, DW_TEMPTY = 3, DW_SFULL = 5, DW_SEMPTY = 6, DW_PFULL = 7, DW_PEMPTY = 8,
-       DW_ACCFULL = 9, DW_BARS = 10 };
+// The Q half and the dO half of a token stage, and the [dM|dN] tile and the A tile, have barriers of their
+// own: each is needed by, and released after, a different MMA chain, and every cycle by which the next
+// load or the next MMA can start earlier shortens the loop load -> recompute -> element-wise -> accumulate.
+enum { DW_WFULL = 0, DW_QFULL = 1, DW_GFULL = 3, DW_QEMPTY = 5, DW_GEMPTY = 7, DW_SFULL = 9, DW_SEMPTY = 10,
+       DW_PFULL = 11, DW_AFULL = 12, DW_PEMPTY = 13, DW_AEMPTY = 14, DW_ACCFULL = 15, DW_BARS = 16 };
 
 struct DwArgs {
     const float *R;
@@ -444,11 +447,18 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     if (threadIdx.x == 0) {
         *abort_flag = (*reinterpret_cast<volatile int *>(args.status) != 0);  // an earlier CTA gave up: drain fast
         mbar_init(bar(DW_WFULL), 1);
-        for (int s = 0; s < L::kTokStages; ++s) { mbar_init(bar(DW_TFULL + s), 1); mbar_init(bar(DW_TEMPTY + s), 1); }
+        for (int s = 0; s < L::kTokStages; ++s) {
+            mbar_init(bar(DW_QFULL + s), 1);
+            mbar_init(bar(DW_GFULL + s), 1);
+            mbar_init(bar(DW_QEMPTY + s), 1);
+            mbar_init(bar(DW_GEMPTY + s), 1);
+        }
         mbar_init(bar(DW_SFULL), 1);
         mbar_init(bar(DW_SEMPTY), kActThreads);
         mbar_init(bar(DW_PFULL), kActThreads);
+        mbar_init(bar(DW_AFULL), kActThreads);
         mbar_init(bar(DW_PEMPTY), 1);
+        mbar_init(bar(DW_AEMPTY), 1);
         mbar_init(bar(DW_ACCFULL), 1);
         fence_mbar_init();
     }
@@ -478,16 +488,19 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 int ts, hh, bb;
                 tile_coords(i, ts, hh, bb);
                 FMHF_TRW(0, i, 0);
-                if (!mbar_wait(bar(DW_TEMPTY + st), ph, ctl, W + 1)) break;
-                FMHF_TRW(0, i, 1);
-                const uint32_t fb = bar(DW_TFULL + st);
-                mbar_arrive_expect_tx(fb, L::kTokStage);
                 const uint32_t d = sTok + st * L::kTokStage;
+                if (!mbar_wait(bar(DW_QEMPTY + st), ph, ctl, W + 1)) break;
+                FMHF_TRW(0, i, 1);
+                const uint32_t fq = bar(DW_QFULL + st);
+                mbar_arrive_expect_tx(fq, L::kTokStage / 2);
 #pragma unroll
-                for (int c = 0; c < L::kChunks; ++c) {
-                    tma_load_4d(d + c * kTile, &tmQ, fb, c * 64, ts * kBT, hh, bb);
-                    tma_load_4d(d + (L::kChunks + c) * kTile, &tmdO, fb, c * 64, ts * kBT, hh, bb);
-                }
+                for (int c = 0; c < L::kChunks; ++c) tma_load_4d(d + c * kTile, &tmQ, fq, c * 64, ts * kBT, hh, bb);
+                if (!mbar_wait(bar(DW_GEMPTY + st), ph, ctl, W + 2)) break;
+                const uint32_t fg = bar(DW_GFULL + st);
+                mbar_arrive_expect_tx(fg, L::kTokStage / 2);
+#pragma unroll
+                for (int c = 0; c < L::kChunks; ++c)
+                    tma_load_4d(d + (L::kChunks + c) * kTile, &tmdO, fg, c * 64, ts * kBT, hh, bb);
                 if (++st == L::kTokStages) { st = 0; ph ^= 1; }
             }
         }
@@ -507,7 +520,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             uint32_t ph = 0;
             for (int i = 0; ok && i < ntiles; ++i) {
                 FMHF_TRW(1, i, 0);
-                if (!mbar_wait(bar(DW_TFULL + st), ph, ctl, W + 4)) break;
+                if (!mbar_wait(bar(DW_QFULL + st), ph, ctl, W + 4)) break;
                 FMHF_TRW(1, i, 1);
                 if (!mbar_wait(bar(DW_SEMPTY), (i & 1) ^ 1, ctl, W + 5)) break;
                 FMHF_TRW(1, i, 2);
@@ -519,6 +532,8 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     umma_ss(tmem + kColS, dq + ((c * kTile + kk * 32) >> 4), dKU + ((c * 2 * kWChunk + kk * 32) >> 4), idS,
                             k > 0 ? 1u : 0u);
                 }
+                if (!mbar_wait(bar(DW_GFULL + st), ph, ctl, W + 4)) break;
+                tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const int c = k >> 2, kk = k & 3;
@@ -549,11 +564,15 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
 #pragma unroll
                 for (int k = 0; k < kBT / 16; ++k)
                     umma_ss(tmem + kColKU, dPmn + k * 128, dq + k * 128, idKU, (i > 0 || k > 0) ? 1u : 0u);
+                umma_commit(bar(DW_QEMPTY + st));  // Q of this stage and the [dM|dN] tile are free
+                umma_commit(bar(DW_PEMPTY));
+                if (!mbar_wait(bar(DW_AFULL), i & 1, ctl, W + 6)) { ok = false; break; }
+                tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < kBT / 16; ++k)
                     umma_ss(tmem + kColV, dAmn + k * 128, dg + k * 128, idV, (i > 0 || k > 0) ? 1u : 0u);
-                umma_commit(bar(DW_TEMPTY + st));
-                umma_commit(bar(DW_PEMPTY));
+                umma_commit(bar(DW_GEMPTY + st));  // dO of this stage and the A tile are free
+                umma_commit(bar(DW_AEMPTY));
                 FMHF_TRW(1, i, 6);
                 if (++st == L::kTokStages) st = 0;
             }
@@ -611,10 +630,15 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 const uint32_t off = sw128_offset(row, half * 4 + q);
                 st_shared_v4(sP + off, pm[4 * q], pm[4 * q + 1], pm[4 * q + 2], pm[4 * q + 3]);
                 st_shared_v4(sP + kTile + off, pn[4 * q], pn[4 * q + 1], pn[4 * q + 2], pn[4 * q + 3]);
-                st_shared_v4(sA + off, pa[4 * q], pa[4 * q + 1], pa[4 * q + 2], pa[4 * q + 3]);
             }
             fence_async_smem();
             mbar_arrive(bar(DW_PFULL));
+            if (!mbar_wait(bar(DW_AEMPTY), (i & 1) ^ 1, ctl, W + 8)) { ok = false; break; }
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                st_shared_v4(sA + sw128_offset(row, half * 4 + q), pa[4 * q], pa[4 * q + 1], pa[4 * q + 2], pa[4 * q + 3]);
+            fence_async_smem();
+            mbar_arrive(bar(DW_AFULL));
             FMHF_TRW(2 + half, i, 4);
         }
         if (ok) ok = mbar_wait(bar(DW_ACCFULL), 0, ctl, W + 9);
