@@ -7,12 +7,12 @@ import threading
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "lib", "libflashmhf_b200.so")
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 BF16, F32_CHECK = 0, 1
 STATIC_SCRATCH_BYTES = 72 << 20
 
-EXPORTS = ("flashmhf_abi_version", "flashmhf_strerror", "flashmhf_last_cuda_error", "flashmhf_forward",
+EXPORTS = ("flashmhf_abi_version", "flashmhf_forward_workspace_bytes", "flashmhf_strerror", "flashmhf_last_cuda_error", "flashmhf_forward",
            "flashmhf_backward_workspace_bytes", "flashmhf_backward", "flashmhf_device_status",
            "flashmhf_launch_count", "flashmhf_profile_begin", "flashmhf_profile_end",
            "flashmhf_backward_static_scratch")
@@ -28,7 +28,8 @@ class Dims(C.Structure):
 
 
 class FwdParams(C.Structure):
-    _fields_ = [("d", Dims), ("Q", Tensor), ("K", Tensor), ("U", Tensor), ("V", Tensor), ("R", Tensor), ("O", Tensor)]
+    _fields_ = [("d", Dims), ("Q", Tensor), ("K", Tensor), ("U", Tensor), ("V", Tensor), ("R", Tensor), ("O", Tensor),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
 class BwdParams(C.Structure):
@@ -65,6 +66,8 @@ def load():
         lib.flashmhf_last_cuda_error.restype = C.c_char_p
         lib.flashmhf_forward.restype = C.c_int
         lib.flashmhf_forward.argtypes = [C.POINTER(FwdParams), C.c_void_p]
+        lib.flashmhf_forward_workspace_bytes.restype = C.c_size_t
+        lib.flashmhf_forward_workspace_bytes.argtypes = [C.POINTER(Dims)]
         lib.flashmhf_backward_workspace_bytes.restype = C.c_size_t
         lib.flashmhf_backward_workspace_bytes.argtypes = [C.POINTER(Dims)]
         lib.flashmhf_backward.restype = C.c_int
@@ -105,7 +108,7 @@ def launch_count():
     return int(load().flashmhf_launch_count())
 
 
-PROFILE_TAGS = {1: "fwd_kernel", 2: "bwd_dq_kernel", 3: "bwd_dw_kernel", 4: "dw_reduce_kernel"}
+PROFILE_TAGS = {1: "fwd_kernel", 2: "bwd_dq_kernel", 3: "bwd_dw_kernel", 4: "dw_reduce_kernel", 5: "o_reduce_kernel"}
 
 
 def profile_begin(max_marks=4096):

@@ -143,6 +143,12 @@ int flashmhf_forward(const flashmhf_fwd_params *p, void *stream) {
     return rc;
 }
 
+size_t flashmhf_forward_workspace_bytes(const flashmhf_dims *d) {
+    if (!d || check_dims(*d) != 0) return 0;
+    if (d->dtype == FLASHMHF_F32_CHECK) return 0;
+    return tc_forward_workspace_bytes(*d);
+}
+
 size_t flashmhf_backward_workspace_bytes(const flashmhf_dims *d) {
     if (!d || check_dims(*d) != 0) return 0;
     if (d->dtype == FLASHMHF_F32_CHECK) return 0;

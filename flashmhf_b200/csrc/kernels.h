@@ -17,6 +17,7 @@ cudaError_t simt_backward(const flashmhf_bwd_params &p, cudaStream_t st, int *n_
 // ---- bf16 tensor-core kernels (tcgen05 / TMEM / TMA) ---------------------------------------
 // Each returns a flashmhf_status (tensor-map encoding can fail with BAD_STRIDE / CUDA).
 int tc_forward(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch);
+size_t tc_forward_workspace_bytes(const flashmhf_dims &d);
 int tc_backward(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch);
 size_t tc_backward_workspace_bytes(const flashmhf_dims &d);
 int tc_backward_static_scratch(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch);
@@ -25,7 +26,7 @@ void set_cuda_error(cudaError_t e, const char *where);
 
 // Kernel-boundary marks for the profiling aid (flashmhf_profile_begin/end): records an event on
 // `st` tagged `tag` when profiling is on, does nothing otherwise.
-enum { kMarkStart = 0, kMarkFwd = 1, kMarkBwdDq = 2, kMarkBwdDw = 3, kMarkBwdReduce = 4 };
+enum { kMarkStart = 0, kMarkFwd = 1, kMarkBwdDq = 2, kMarkBwdDw = 3, kMarkBwdReduce = 4, kMarkFwdReduce = 5 };
 void prof_mark(cudaStream_t st, int tag);
 
 }  // namespace fmhf

@@ -66,18 +66,29 @@ struct FwdSmem {
     static constexpr uint32_t kOffKU = kOffQ + kQBytes;
     static constexpr uint32_t kOffV = kOffKU + kRing * kKUStage;
     static constexpr uint32_t kOffBar = kOffV + kRing * kVStage;
-    static constexpr uint32_t kTotal = kOffBar + 256 + 1024;  // + barriers/control + alignment slack
+    static constexpr uint32_t kTotal = kOffBar + 320 + 1024;  // + barriers/control + alignment slack
 };
 
 // barrier slots (8 bytes each) inside the control area
 // SFULL: S computed; AFULL: A written over it; SFREE: O += A V done, buffer reusable
-enum { BAR_Q = 0, BAR_KUFULL = 1, BAR_KUEMPTY = 5, BAR_VFULL = 9, BAR_VEMPTY = 13, BAR_SFULL = 17, BAR_AFULL = 20,
-       BAR_SFREE = 23, BAR_OFULL = 26, BAR_COUNT = 27 };
+// The three S-buffer barriers exist in 2 * kDepth copies, indexed by block % (2 * kDepth).  Blocks of
+// even and odd index are handled by different threads (two S issuers, two activation warpgroups), so
+// with one barrier per buffer a waiter would see only every other phase of it, and a one-bit phase
+// parity cannot tell "two phases behind" from "done".  With 2 * kDepth barriers every barrier has one
+// fixed waiter that observes each of its phases.
+enum { BAR_Q = 0, BAR_KUFULL = 1, BAR_KUEMPTY = 5, BAR_VFULL = 9, BAR_VEMPTY = 13, BAR_SFULL = 17, BAR_AFULL = 23,
+       BAR_SFREE = 29, BAR_OFULL = 35, BAR_COUNT = 36 };
+constexpr int kSBars = 2 * kDepth;
 
 struct FwdArgs {
     const float *R;
     long long r_sb, r_sh, r_ss;
     int S, E, De, G;
+    // Split of the intermediate dimension over CTAs (short token counts, e.g. decode): CTA x handles
+    // blocks [isplit * blocks_per_split, ...) of tile x / nsplit and writes an fp32 partial O.
+    int nsplit, blocks_per_split;
+    float *part;           // [nsplit][B][H][S][DH] fp32, used when nsplit > 1
+    int H;
     int *status;
 };
 
@@ -108,9 +119,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     auto bar = [&](int i) { return sBar + 8u * i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t0 = blockIdx.x * kBT, h = blockIdx.y, b = blockIdx.z, hk = h / args.G;
+    const int tile = blockIdx.x / args.nsplit, isplit = blockIdx.x - tile * args.nsplit;
+    const int t0 = tile * kBT, h = blockIdx.y, b = blockIdx.z, hk = h / args.G;
     const int blocks_per_e = args.De / kBI;
-    const int nblk = args.E * blocks_per_e;
+    const int j0 = isplit * args.blocks_per_split;                          // first block of this CTA
+    const int nblk = min(args.E * blocks_per_e - j0, args.blocks_per_split);  // blocks of this CTA (>= 1)
     const WaitCtl ctl{abort_flag, args.status};
     constexpr int W = kKernelFwd * 100;
 
@@ -123,7 +136,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             mbar_init(bar(BAR_VFULL + i), 1);
             mbar_init(bar(BAR_VEMPTY + i), 1);
         }
-        for (int i = 0; i < kDepth; ++i) {
+        for (int i = 0; i < kSBars; ++i) {
             mbar_init(bar(BAR_SFULL + i), 1);
             mbar_init(bar(BAR_AFULL + i), kGroupThreads);
             mbar_init(bar(BAR_SFREE + i), 1);
@@ -162,8 +175,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     mbar_arrive_expect_tx(fku, L::kKUStage);
 #pragma unroll
                     for (int c = 0; c < L::kChunks; ++c) {
-                        tma_load_3d(dku + c * 2 * L::kWChunk, &tmK, fku, c * 64, j * kBI, hk);
-                        tma_load_3d(dku + c * 2 * L::kWChunk + L::kWChunk, &tmU, fku, c * 64, j * kBI, hk);
+                        tma_load_3d(dku + c * 2 * L::kWChunk, &tmK, fku, c * 64, (j0 + j) * kBI, hk);
+                        tma_load_3d(dku + c * 2 * L::kWChunk + L::kWChunk, &tmU, fku, c * 64, (j0 + j) * kBI, hk);
                     }
                     pk.advance(1);
                 }
@@ -173,7 +186,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     mbar_arrive_expect_tx(fv, L::kVStage);
 #pragma unroll
                     for (int c = 0; c < L::kChunks; ++c)
-                        tma_load_3d(dv + c * L::kWChunk, &tmV, fv, c * 64, (j - 2) * kBI, hk);
+                        tma_load_3d(dv + c * L::kWChunk, &tmV, fv, c * 64, (j0 + j - 2) * kBI, hk);
                     pv.advance(1);
                 }
             }
@@ -191,18 +204,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             const int first = warp - 1;
             bool ok = mbar_wait(bar(BAR_Q), 0, ctl, W + 3);
             RingPos<kRing> pw;   // [K;U] stage of block j
-            RingPos<kDepth> ps;  // S buffer of block j
+            RingPos<kSBars> ps;  // barrier set of block j; its S buffer is ps.slot % kDepth
+            RingPos<kSBars> pf;  // barrier set of block j - kDepth, the previous user of that buffer
+            pf.lap = 1;          // so that the lap parity is 0 once j - kDepth reaches 0
             pw.advance(first);
             ps.advance(first);
+            pf.advance(first + kDepth);
             for (int j = first; ok && j < nblk; j += 2) {
                 FMHF_TR(1, j, 0);
                 if (!mbar_wait(bar(BAR_KUFULL + pw.slot), pw.lap, ctl, W + 4)) break;
                 FMHF_TR(1, j, 1);
-                if (!mbar_wait(bar(BAR_SFREE + ps.slot), ps.lap ^ 1, ctl, W + 5)) break;
+                if (j >= kDepth && !mbar_wait(bar(BAR_SFREE + pf.slot), pf.lap, ctl, W + 5)) break;
                 FMHF_TR(1, j, 2);
                 tc_fence_after();
                 const uint64_t dku = dKU0 + pw.slot * kKUStep;
-                const uint32_t tS = tmem + kColS0 + ps.slot * kColSStride;
+                const uint32_t tS = tmem + kColS0 + (ps.slot >= kDepth ? ps.slot - kDepth : ps.slot) * kColSStride;
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const int c = k >> 2, kk = k & 3;
@@ -214,6 +230,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 FMHF_TR(1, j, 3);
                 pw.advance(2);
                 ps.advance(2);
+                pf.advance(2);
             }
         }
     } else if (warp == 3) {
@@ -225,7 +242,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             const uint64_t dV0 = desc_mnmajor(sV, L::kWChunk);
             constexpr uint64_t kVStep = L::kVStage >> 4;
             RingPos<kRing> pw;
-            RingPos<kDepth> ps;
+            RingPos<kSBars> ps;
             bool ok = true;
             for (int j = 0; j < nblk; ++j) {
                 if (!mbar_wait(bar(BAR_VFULL + pw.slot), pw.lap, ctl, W + 6)) { ok = false; break; }
@@ -233,7 +250,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 FMHF_TR(1, j, 4);
                 tc_fence_after();
                 const uint64_t dv = dV0 + pw.slot * kVStep;
-                const uint32_t tA = tmem + kColS0 + ps.slot * kColSStride;
+                const uint32_t tA = tmem + kColS0 + (ps.slot >= kDepth ? ps.slot - kDepth : ps.slot) * kColSStride;
 #pragma unroll
                 for (int k = 0; k < kBI / 16; ++k)
                     umma_ts(tmem + kColO, tA + k * 8, dv + k * 128, idesc2, (j > 0 || k > 0) ? 1u : 0u);
@@ -255,10 +272,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
         bool ok = true;
         // sub-network of this group's current block and position inside it; routing weight fetched a block ahead
-        int e = 0, in_e = group;
-        while (in_e >= blocks_per_e) { in_e -= blocks_per_e; ++e; }
+        int e = (j0 + group) / blocks_per_e, in_e = (j0 + group) - e * blocks_per_e;
         float r_cur = (in_range && e < args.E) ? __ldg(rrow + e) : 0.f;
-        RingPos<kDepth> p;
+        RingPos<kSBars> p;
         p.advance(group);
         for (int j = group; j < nblk; j += 2) {
             int e_nb = e, in_nb = in_e + 2;  // where this group's next block lies
@@ -269,7 +285,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             if (!mbar_wait(bar(BAR_SFULL + p.slot), p.lap, ctl, W + 8)) { ok = false; break; }
             FMHF_TR(2 + group, j, 1);
             tc_fence_after();
-            const uint32_t ts = lane_base + kColS0 + p.slot * kColSStride;
+            const uint32_t ts = lane_base + kColS0 + (p.slot >= kDepth ? p.slot - kDepth : p.slot) * kColSStride;
             uint32_t a[32];  // 64 bf16 of this row of A
 #pragma unroll
             for (int part = 0; part < 2; ++part) {
@@ -293,7 +309,26 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
         // epilogue: O (fp32, tensor memory) -> bf16 -> shared (over the Q tile) -> TMA store
         if (ok) ok = mbar_wait(bar(BAR_OFULL), 0, ctl, W + 10);
-        if (ok) {
+        if (ok && args.nsplit > 1) {
+            // partial O of this CTA's blocks, fp32, straight from tensor memory to the workspace
+            tc_fence_after();
+            constexpr int kColsPerGroup = DH / 2;
+            const int c0 = group * kColsPerGroup;
+            float *dst = args.part + ((((long long)isplit * gridDim.z + b) * args.H + h) * args.S + t) * DH + c0;
+#pragma unroll
+            for (int g = 0; g < kColsPerGroup / 16; ++g) {
+                uint32_t o[16];
+                tmem_ld16_sync(lane_base + kColO + c0 + g * 16, o);
+                if (in_range) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v)
+                        *reinterpret_cast<float4 *>(dst + g * 16 + v * 4) =
+                            make_float4(__uint_as_float(o[4 * v]), __uint_as_float(o[4 * v + 1]),
+                                        __uint_as_float(o[4 * v + 2]), __uint_as_float(o[4 * v + 3]));
+                }
+            }
+            tc_fence_before();
+        } else if (ok) {
             tc_fence_after();
             constexpr int kColsPerGroup = DH / 2;  // 64, 48 or 32 columns per thread
             const int c0 = group * kColsPerGroup;
@@ -315,7 +350,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             fence_async_smem();
         }
         named_bar_sync(1, 2 * kGroupThreads);
-        if (ok && warp == 4 && lane == 0 && !*abort_flag) {
+        if (ok && args.nsplit == 1 && warp == 4 && lane == 0 && !*abort_flag) {
             for (int c = 0; c < L::kChunks; ++c) tma_store_4d(&tmO, sQ + c * (kBT * 128), c * 64, t0, h, b);
             tma_store_commit();
             tma_store_wait_all();
@@ -338,6 +373,52 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     }
 }
 
+// O = bf16(sum of the partial O of the splits, in split order); 4 elements per thread.
+struct OReduceArgs {
+    const float *part;
+    long long plane;  // B*H*S*DH
+    __nv_bfloat16 *O;
+    long long s_b, s_h, s_s;
+    int nsplit, H, S, DH;
+};
+__global__ void __launch_bounds__(256) o_reduce_kernel(const OReduceArgs a) {
+    const long long n4 = a.plane / 4;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n4;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long el = idx * 4;
+        float4 acc = *reinterpret_cast<const float4 *>(a.part + el);
+        for (int s = 1; s < a.nsplit; ++s) {
+            const float4 v = *reinterpret_cast<const float4 *>(a.part + (long long)s * a.plane + el);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const int c = (int)(el % a.DH);
+        const long long r1 = el / a.DH;
+        const int t = (int)(r1 % a.S);
+        const long long r2 = r1 / a.S;
+        const int h = (int)(r2 % a.H);
+        const long long b = r2 / a.H;
+        *reinterpret_cast<uint2 *>(a.O + b * a.s_b + h * a.s_h + t * a.s_s + c) =
+            make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+    }
+}
+
+struct FwdPlan {
+    int nsplit, blocks_per_split;
+};
+// With fewer token tiles than about half the SMs (decode-shaped calls) the blocks of the intermediate
+// dimension are spread over several CTAs per tile so that the weights stream in at full machine rate.
+FwdPlan fwd_plan(const flashmhf_dims &d) {
+    const long long tiles = (long long)((d.S + kBT - 1) / kBT) * d.H * d.B;
+    const int nblk = d.E * d.De / kBI;
+    int ns = 1;
+    if (tiles < 74) ns = (int)((148 + tiles - 1) / tiles);
+    if (ns > nblk) ns = nblk;
+    FwdPlan p;
+    p.blocks_per_split = (nblk + ns - 1) / ns;
+    p.nsplit = (nblk + p.blocks_per_split - 1) / p.blocks_per_split;  // no empty split
+    return p;
+}
+
 template <int DH>
 int launch_fwd(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
     using L = FwdSmem<DH>;
@@ -352,19 +433,44 @@ int launch_fwd(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
         cudaError_t e = cudaFuncSetAttribute(fwd_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
         if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(fwd_kernel)"); return FLASHMHF_ERR_CUDA; }
     }
+    const FwdPlan pl = fwd_plan(p.d);
+    if (pl.nsplit > 1) {
+        if (!p.workspace || p.workspace_bytes < tc_forward_workspace_bytes(p.d) ||
+            (reinterpret_cast<uintptr_t>(p.workspace) & 255u))
+            return FLASHMHF_ERR_WORKSPACE;
+        if (p.O.stride[2] % 4 != 0 || p.O.stride[1] % 4 != 0 || p.O.stride[0] % 4 != 0) return FLASHMHF_ERR_BAD_STRIDE;
+    }
     FwdArgs a{static_cast<const float *>(p.R.ptr), p.R.stride[0], p.R.stride[1], p.R.stride[2],
-              p.d.S, p.d.E, p.d.De, p.d.H / p.d.Hkuv, device_status_ptr()};
-    dim3 grid((p.d.S + kBT - 1) / kBT, p.d.H, p.d.B);
+              p.d.S, p.d.E, p.d.De, p.d.H / p.d.Hkuv, pl.nsplit, pl.blocks_per_split,
+              static_cast<float *>(p.workspace), p.d.H, device_status_ptr()};
+    dim3 grid(((p.d.S + kBT - 1) / kBT) * pl.nsplit, p.d.H, p.d.B);
     prof_mark(st, kMarkStart);
     fwd_kernel<DH><<<grid, kThreads, L::kTotal, st>>>(tmQ, tmK, tmU, tmV, tmO, a);
     prof_mark(st, kMarkFwd);
     *n_launch += 1;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_cuda_error(e, "fwd_kernel launch"); return FLASHMHF_ERR_CUDA; }
+    if (pl.nsplit > 1) {
+        const long long plane = (long long)p.d.B * p.d.H * p.d.S * DH;
+        OReduceArgs ra{static_cast<const float *>(p.workspace), plane, static_cast<__nv_bfloat16 *>(p.O.ptr),
+                       p.O.stride[0], p.O.stride[1], p.O.stride[2], pl.nsplit, p.d.H, p.d.S, DH};
+        const long long n4 = plane / 4;
+        const int blocks = (int)((n4 + 255) / 256 < 148 * 4 ? (n4 + 255) / 256 : 148 * 4);
+        o_reduce_kernel<<<blocks, 256, 0, st>>>(ra);
+        prof_mark(st, kMarkFwdReduce);
+        *n_launch += 1;
+        if ((e = cudaGetLastError()) != cudaSuccess) { set_cuda_error(e, "o_reduce_kernel launch"); return FLASHMHF_ERR_CUDA; }
+    }
     return FLASHMHF_OK;
 }
 
 }  // namespace
+
+size_t tc_forward_workspace_bytes(const flashmhf_dims &d) {
+    const FwdPlan pl = fwd_plan(d);
+    if (pl.nsplit <= 1) return 0;
+    return (size_t)pl.nsplit * (size_t)d.B * d.H * d.S * d.Dh * sizeof(float);
+}
 
 int tc_forward(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
     switch (p.d.Dh) {

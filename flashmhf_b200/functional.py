@@ -64,6 +64,12 @@ def _dims(B, H, S, dh, hk, E, de, dtype):
     return _lib.Dims(B, H, S, dh, hk, E, de, _DT[dtype])
 
 
+def _tokens_as_sequence(*ts):
+    """Decode-shaped call (S == 1, B > 1): view [B,H,1,X] tensors as [1,H,B,X] -- a pure permutation, no copy --
+    so that the B token rows share tiles instead of occupying one 128-row tile each."""
+    return [t.permute(2, 1, 0, 3) for t in ts]
+
+
 def forward_raw(Q, K, U, V, R, out=None):
     """O = flashmhf_forward(...) on the current stream; no autograd."""
     B, H, S, dh, hk, E, de = _validate(Q, K, U, V, R)
@@ -73,8 +79,18 @@ def forward_raw(Q, K, U, V, R, out=None):
     if R.stride(-1) != 1:
         R = R.contiguous()
     O = torch.empty_like(Q, memory_format=torch.contiguous_format) if out is None else out
-    p = _lib.FwdParams(_dims(B, H, S, dh, hk, E, de, Q.dtype), _tensor(Q), _tensor(K), _tensor(U), _tensor(V),
-                       _tensor(R), _tensor(O))
+    Qk, Rk, Ok = Q, R, O
+    if S == 1 and B > 1:
+        Qk, Rk, Ok = _tokens_as_sequence(Q, R, O)
+        if all(_strided_ok(t, False, 0) for t in (Qk, Ok)):
+            B, S = 1, B
+        else:
+            Qk, Rk, Ok = Q, R, O
+    d = _dims(B, H, S, dh, hk, E, de, Q.dtype)
+    nbytes = int(lib.flashmhf_forward_workspace_bytes(C.byref(d)))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=Q.device) if nbytes else None
+    p = _lib.FwdParams(d, _tensor(Qk), _tensor(K), _tensor(U), _tensor(V), _tensor(Rk), _tensor(Ok),
+                       ws.data_ptr() if nbytes else None, nbytes)
     with torch.cuda.device(Q.device):
         _lib.check(lib.flashmhf_forward(C.byref(p), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return O

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define FLASHMHF_ABI_VERSION 1
+#define FLASHMHF_ABI_VERSION 2
 
 typedef enum flashmhf_status {
     FLASHMHF_OK = 0,
@@ -69,6 +69,8 @@ typedef struct flashmhf_fwd_params {
     flashmhf_dims d;
     flashmhf_tensor Q, K, U, V, R; /* inputs */
     flashmhf_tensor O;             /* output, every element written; no pre-zeroing needed */
+    void *workspace;               /* device scratch, 256-byte aligned; needed only when                 */
+    size_t workspace_bytes;        /* flashmhf_forward_workspace_bytes() > 0 (short token counts), else NULL/0 */
 } flashmhf_fwd_params;
 
 typedef struct flashmhf_bwd_params {
@@ -94,6 +96,13 @@ const char *flashmhf_last_cuda_error(void);
  * device and returns.  Replaces flashffn_moe_forward, flash_ffn_moe.cu:938-1007, and the launch at
  * kernels/triton/flash_mlp_moe.py:777-790. */
 int flashmhf_forward(const flashmhf_fwd_params *p, void *stream);
+
+/* Bytes of scratch flashmhf_forward needs for these dims.  0 unless there are fewer token tiles
+ * (ceil(S/128) * H * B) than about half the SMs -- the decode-shaped case (reference: batched decode
+ * through the same call, models/flashmhf/modeling_mhffnmoe.py:406-408) -- where the intermediate
+ * dimension is split over CTAs and fp32 partial outputs are summed in a fixed order.  Pure host
+ * arithmetic.  Reference counterpart: none. */
+size_t flashmhf_forward_workspace_bytes(const flashmhf_dims *d);
 
 /* Bytes of scratch flashmhf_backward needs for these dims (0 is possible).  Pure host arithmetic. */
 size_t flashmhf_backward_workspace_bytes(const flashmhf_dims *d);
@@ -135,7 +144,8 @@ int flashmhf_device_status(int *code);
  * call records a CUDA event on its stream before its first kernel and after each kernel (no
  * synchronisation, up to `max_marks` events in total).  flashmhf_profile_end is SYNCHRONOUS: it
  * waits for the device and returns, for each kernel launched in between, its duration in
- * milliseconds and a tag (1 forward, 2 backward dQ/dR, 3 backward dK/dU/dV, 4 split reduction).
+ * milliseconds and a tag (1 forward, 2 backward dQ/dR, 3 backward dK/dU/dV, 4 backward split
+ * reductions, 5 forward split reduction).
  * One profiling session at a time, calls from one stream.  Reference counterpart: none. */
 int flashmhf_profile_begin(int max_marks);
 int flashmhf_profile_end(float *ms, int *tags, int capacity, int *n_out);

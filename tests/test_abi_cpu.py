@@ -29,7 +29,7 @@ def test_loader_lists_every_declared_function():
 
 
 def test_abi_version_and_strerror(lib):
-    assert lib.flashmhf_abi_version() == 1
+    assert lib.flashmhf_abi_version() == 2
     assert lib.flashmhf_strerror(0) == b"ok"
     for code in range(-11, 0):
         assert len(lib.flashmhf_strerror(code)) > 3
@@ -39,7 +39,7 @@ def test_struct_layout_matches_header():
     """sizeof of the ctypes mirrors equals what the C compiler lays out (8 int32 + tensors of 4 x 8 bytes)."""
     from flashmhf_b200 import _lib
     assert C.sizeof(_lib.Dims) == 32 and C.sizeof(_lib.Tensor) == 32
-    assert C.sizeof(_lib.FwdParams) == 32 + 6 * 32
+    assert C.sizeof(_lib.FwdParams) == 32 + 6 * 32 + 16
     assert C.sizeof(_lib.BwdParams) == 32 + 11 * 32 + 16
 
 
@@ -67,6 +67,16 @@ def test_workspace_bytes_is_pure_arithmetic(lib):
     assert n % per_split == 0 and 1 <= n // per_split <= 16
     d.dtype = 1
     assert lib.flashmhf_backward_workspace_bytes(C.byref(d)) == 0
+
+
+def test_forward_workspace_only_for_short_token_counts(lib):
+    from flashmhf_b200 import _lib
+    big = _lib.Dims(16, 8, 2048, 128, 8, 11, 256, 0)       # 2048 tiles: no split, no scratch
+    assert lib.flashmhf_forward_workspace_bytes(C.byref(big)) == 0
+    dec = _lib.Dims(1, 16, 64, 128, 16, 22, 256, 0)        # 1.3B decode: 16 tiles -> intermediate dimension split
+    n = lib.flashmhf_forward_workspace_bytes(C.byref(dec))
+    per_split = 1 * 16 * 64 * 128 * 4
+    assert n % per_split == 0 and 2 <= n // per_split <= 88
 
 
 def test_python_wrapper_rejects_bad_arguments_on_cpu():

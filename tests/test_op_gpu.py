@@ -79,6 +79,24 @@ def test_bf16_backward(shape):
         assert orc.rel_l2(a, b) < TOL_BF16, name
 
 
+@pytest.mark.parametrize("shape", [(64, 16, 16, 1, 128, 22, 256),   # 1.3B batched decode: 64 sequences, one new token each
+                                   (1, 2, 2, 100, 128, 4, 128),     # one short tile, two heads
+                                   (3, 1, 1, 1, 96, 3, 64),         # three single-token rows, d_h = 96
+                                   (1, 4, 2, 64, 64, 5, 192)])      # shared K/U/V heads
+def test_bf16_forward_short_token_counts_split_path(shape):
+    """Fewer token tiles than SMs: the intermediate dimension is split over CTAs (fp32 partial outputs,
+    fixed-order sum); decode-shaped [B,H,1,d_h] inputs are viewed as one sequence of B tokens."""
+    import flashmhf_b200 as fm
+    B, H, Hk, S, dh, E, de = shape
+    Q, K, U, V, R = orc.make_op_inputs(B, H, S, dh, E, de, Hkuv=Hk, seed=22, dtype=torch.bfloat16, with_dO=False)
+    out = torch.full(Q.shape, float("nan"), dtype=torch.bfloat16, device="cuda")
+    O = fm.forward_raw(*_dev([Q, K, U, V, R]), out=out).cpu().float()
+    assert torch.isfinite(O).all()
+    assert orc.rel_l2(O, orc.mhffn_forward(Q.float(), K.float(), U.float(), V.float(), R)) < TOL_BF16
+    again = fm.forward_raw(*_dev([Q, K, U, V, R])).cpu().float()
+    assert torch.equal(O, again)
+
+
 def test_autograd_function_matches_oracle_autograd():
     import flashmhf_b200 as fm
     Q, K, U, V, R, dO = orc.make_op_inputs(2, 2, 192, 128, 2, 64, seed=14, dtype=torch.bfloat16)
@@ -154,7 +172,8 @@ def test_argument_errors_are_python_exceptions():
 
 def test_large_shape_linearity_property():
     """At the 370M layer's full token count: O is linear in R, so O(R1) + O(R2) == O(R1 + R2) up to bf16 rounding,
-    and a tile-aligned slice of a big batch equals the same rows computed alone (bitwise)."""
+    and a tile-aligned slice of a big batch equals the same rows computed alone (bitwise; the slice is large
+    enough -- 128 token tiles -- not to take the split path for short token counts, which sums in another order)."""
     import flashmhf_b200 as fm
     B, H, S, dh, E, de = 4, 8, 2048, 128, 11, 256
     g = torch.Generator(device="cuda").manual_seed(19)
@@ -164,5 +183,5 @@ def test_large_shape_linearity_property():
     R2 = torch.rand(B, H, S, E, device="cuda", generator=g)
     O1, O2, O12 = (fm.forward_raw(Q, K, U, V, r).float() for r in (R1, R2, R1 + R2))
     assert orc.rel_l2((O1 + O2).cpu(), O12.cpu()) < TOL_BF16
-    sub = fm.forward_raw(Q[1:2, :, 256:1280].contiguous(), K, U, V, R1[1:2, :, 256:1280].contiguous())
-    assert torch.equal(sub, fm.forward_raw(Q, K, U, V, R1)[1:2, :, 256:1280])
+    sub = fm.forward_raw(Q[1:3, :, 256:1280].contiguous(), K, U, V, R1[1:3, :, 256:1280].contiguous())
+    assert torch.equal(sub, fm.forward_raw(Q, K, U, V, R1)[1:3, :, 256:1280])
