@@ -5,7 +5,10 @@ import sys
 
 from .functional import FlashMHFFunction, backward_raw, flash_mhf, forward_raw  # noqa: F401
 
-__all__ = ["flash_mhf", "FlashMHFFunction", "forward_raw", "backward_raw", "install_reference_seam"]
+from .layer import expert_views, fused_prologue, mhffn_layer  # noqa: F401,E402
+
+__all__ = ["flash_mhf", "FlashMHFFunction", "forward_raw", "backward_raw", "install_reference_seam",
+           "fused_prologue", "mhffn_layer", "expert_views"]
 
 
 def install_reference_seam():

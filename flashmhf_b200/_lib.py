@@ -15,7 +15,8 @@ STATIC_SCRATCH_BYTES = 72 << 20
 EXPORTS = ("flashmhf_abi_version", "flashmhf_forward_workspace_bytes", "flashmhf_strerror", "flashmhf_last_cuda_error", "flashmhf_forward",
            "flashmhf_backward_workspace_bytes", "flashmhf_backward", "flashmhf_device_status",
            "flashmhf_launch_count", "flashmhf_profile_begin", "flashmhf_profile_end",
-           "flashmhf_backward_static_scratch")
+           "flashmhf_backward_static_scratch", "flashmhf_prologue_forward",
+           "flashmhf_prologue_backward_workspace_bytes", "flashmhf_prologue_backward")
 
 
 class Tensor(C.Structure):
@@ -35,6 +36,18 @@ class FwdParams(C.Structure):
 class BwdParams(C.Structure):
     _fields_ = [("d", Dims), ("Q", Tensor), ("K", Tensor), ("U", Tensor), ("V", Tensor), ("R", Tensor),
                 ("dO", Tensor), ("dQ", Tensor), ("dK", Tensor), ("dU", Tensor), ("dV", Tensor), ("dR", Tensor),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
+class PrologueParams(C.Structure):
+    _fields_ = [("B", C.c_int32), ("S", C.c_int32), ("H", C.c_int32), ("Dh", C.c_int32), ("E", C.c_int32),
+                ("eps", C.c_float), ("X", C.c_void_p), ("x_token_stride", C.c_int64), ("norm_weight", C.c_void_p),
+                ("router", C.c_void_p), ("Q", C.c_void_p), ("R", C.c_void_p)]
+
+
+class PrologueBwdParams(C.Structure):
+    _fields_ = [("fwd", PrologueParams), ("dQ", C.c_void_p), ("dq_stride", C.c_int64 * 3), ("dR", C.c_void_p),
+                ("dX", C.c_void_p), ("d_router", C.c_void_p), ("d_norm_weight", C.c_void_p),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
 
 
@@ -74,6 +87,12 @@ def load():
         lib.flashmhf_backward.argtypes = [C.POINTER(BwdParams), C.c_void_p]
         lib.flashmhf_backward_static_scratch.restype = C.c_int
         lib.flashmhf_backward_static_scratch.argtypes = [C.POINTER(BwdParams), C.c_void_p]
+        lib.flashmhf_prologue_forward.restype = C.c_int
+        lib.flashmhf_prologue_forward.argtypes = [C.POINTER(PrologueParams), C.c_void_p]
+        lib.flashmhf_prologue_backward_workspace_bytes.restype = C.c_size_t
+        lib.flashmhf_prologue_backward_workspace_bytes.argtypes = [C.POINTER(PrologueParams)]
+        lib.flashmhf_prologue_backward.restype = C.c_int
+        lib.flashmhf_prologue_backward.argtypes = [C.POINTER(PrologueBwdParams), C.c_void_p]
         lib.flashmhf_device_status.restype = C.c_int
         lib.flashmhf_device_status.argtypes = [C.POINTER(C.c_int)]
         lib.flashmhf_launch_count.restype = C.c_uint64
@@ -108,7 +127,8 @@ def launch_count():
     return int(load().flashmhf_launch_count())
 
 
-PROFILE_TAGS = {1: "fwd_kernel", 2: "bwd_dq_kernel", 3: "bwd_dw_kernel", 4: "dw_reduce_kernel", 5: "o_reduce_kernel"}
+PROFILE_TAGS = {1: "fwd_kernel", 2: "bwd_dq_kernel", 3: "bwd_dw_kernel", 4: "dw_reduce_kernel", 5: "o_reduce_kernel",
+                6: "prologue_fwd_kernel", 7: "prologue_bwd_kernel", 8: "prologue_reduce_kernel"}
 
 
 def profile_begin(max_marks=4096):

@@ -198,6 +198,31 @@ int flashmhf_backward_static_scratch(const flashmhf_bwd_params *p, void *stream)
     return rc;
 }
 
+int flashmhf_prologue_forward(const flashmhf_prologue_params *p, void *stream) {
+    if (!p) return FLASHMHF_ERR_NULL;
+    int rc = check_arch();
+    if (rc) return rc;
+    int n = 0;
+    rc = prologue_forward(*p, static_cast<cudaStream_t>(stream), &n);
+    g_launches += (uint64_t)n;
+    return rc;
+}
+
+size_t flashmhf_prologue_backward_workspace_bytes(const flashmhf_prologue_params *p) {
+    if (!p || p->B < 1 || p->S < 1 || p->H < 1 || p->E < 1 || p->Dh < 1) return 0;
+    return prologue_backward_workspace_bytes(*p);
+}
+
+int flashmhf_prologue_backward(const flashmhf_prologue_bwd_params *p, void *stream) {
+    if (!p) return FLASHMHF_ERR_NULL;
+    int rc = check_arch();
+    if (rc) return rc;
+    int n = 0;
+    rc = prologue_backward(*p, static_cast<cudaStream_t>(stream), &n);
+    g_launches += (uint64_t)n;
+    return rc;
+}
+
 int flashmhf_profile_begin(int max_marks) {
     std::lock_guard<std::mutex> lk(g_mu);
     if (g_prof.on || max_marks < 2) return FLASHMHF_ERR_BAD_SHAPE;

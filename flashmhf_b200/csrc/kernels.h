@@ -22,11 +22,17 @@ int tc_backward(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch);
 size_t tc_backward_workspace_bytes(const flashmhf_dims &d);
 int tc_backward_static_scratch(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch);
 
+// ---- fused layer prologue (per-head RMSNorm + router weights), HBM-bound CUDA-core kernels --
+int prologue_forward(const flashmhf_prologue_params &p, cudaStream_t st, int *n_launch);
+size_t prologue_backward_workspace_bytes(const flashmhf_prologue_params &p);
+int prologue_backward(const flashmhf_prologue_bwd_params &p, cudaStream_t st, int *n_launch);
+
 void set_cuda_error(cudaError_t e, const char *where);
 
 // Kernel-boundary marks for the profiling aid (flashmhf_profile_begin/end): records an event on
 // `st` tagged `tag` when profiling is on, does nothing otherwise.
-enum { kMarkStart = 0, kMarkFwd = 1, kMarkBwdDq = 2, kMarkBwdDw = 3, kMarkBwdReduce = 4, kMarkFwdReduce = 5 };
+enum { kMarkStart = 0, kMarkFwd = 1, kMarkBwdDq = 2, kMarkBwdDw = 3, kMarkBwdReduce = 4, kMarkFwdReduce = 5,
+       kMarkPrologueFwd = 6, kMarkPrologueBwd = 7, kMarkPrologueReduce = 8 };
 void prof_mark(cudaStream_t st, int tag);
 
 }  // namespace fmhf

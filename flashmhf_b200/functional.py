@@ -78,7 +78,7 @@ def forward_raw(Q, K, U, V, R, out=None):
     R = R.to(torch.float32)
     if R.stride(-1) != 1:
         R = R.contiguous()
-    O = torch.empty_like(Q, memory_format=torch.contiguous_format) if out is None else out
+    O = torch.empty_like(Q) if out is None else out  # keeps Q's memory layout ([B,H,S,d] or [B,S,H,d])
     Qk, Rk, Ok = Q, R, O
     if S == 1 and B > 1:
         Qk, Rk, Ok = _tokens_as_sequence(Q, R, O)
@@ -107,7 +107,7 @@ def backward_raw(Q, K, U, V, R, dO):
     R = R.to(torch.float32)
     if R.stride(-1) != 1:
         R = R.contiguous()
-    dQ = torch.empty_like(Q, memory_format=torch.contiguous_format)
+    dQ = torch.empty_like(Q)  # keeps Q's memory layout
     dK, dU, dV = (torch.empty_like(t, memory_format=torch.contiguous_format) for t in (K, U, V))
     dR = torch.empty((B, H, S, E), dtype=torch.float32, device=Q.device)
     d = _dims(B, H, S, dh, hk, E, de, Q.dtype)

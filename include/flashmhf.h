@@ -126,14 +126,50 @@ int flashmhf_backward(const flashmhf_bwd_params *p, void *stream);
  *   - bf16 only.  Dims whose flashmhf_backward_workspace_bytes() exceeds the array are refused
  *     with FLASHMHF_ERR_SCRATCH_LIMIT; nothing is launched.
  *   - The call makes no cudaMalloc, cudaFree or other allocating call.  Its FIRST call on a device
- *     looks up the array's device address (once per device, with that device current); make that
- *     first call before any stream capture.
+ *     looks up the array's device address (once per device, with that device current).
  *   - All calls on a device share the one array and it keeps the previous call's contents.  The
  *     kernels overwrite everything they later read, so stale contents are harmless, but two calls
  *     whose kernels overlap on the GPU (different streams, no ordering between them) race on it:
  *     order them, or use flashmhf_backward with separate workspaces.
  * This entry point has no counterpart in the reference. */
 int flashmhf_backward_static_scratch(const flashmhf_bwd_params *p, void *stream);
+
+/* ---- Fused layer prologue (optional companion of the operator) ------------------------------
+ * What the reference layer does between its first projection and the operator, in one kernel
+ * (models/flashmhf/modeling_mhffnmoe.py:362-386; per-head RMSNorm :116-135):
+ *   X [B,S,H,d_h] bf16 (token stride x_token_stride >= H*d_h elements)
+ *     -> Q = bf16(RMSNorm_h(X) * norm_weight[h,:])  written at the same offsets as X, i.e. in [B,S,H,d_h]
+ *        layout (skipped when norm_weight is NULL: then Q is X itself); the operator reads it in place
+ *        through flashmhf_tensor strides (B: S*x_token_stride, H: d_h, S: x_token_stride), no transposing copy
+ *     -> R [B,H,S,E] fp32 = sigmoid(float(Q) . router[h]) normalised over E (denominator clamped at 1e-20)
+ * d_h in {64, 96, 128}, E <= 32.  norm_weight [H,d_h] and router [H,d_h,E] are fp32. */
+typedef struct flashmhf_prologue_params {
+    int32_t B, S, H, Dh, E;
+    float eps;
+    const void *X;
+    int64_t x_token_stride;
+    const float *norm_weight; /* NULL = no RMSNorm */
+    const float *router;
+    void *Q;                  /* bf16, same layout as X; ignored when norm_weight is NULL */
+    float *R;
+} flashmhf_prologue_params;
+
+typedef struct flashmhf_prologue_bwd_params {
+    flashmhf_prologue_params fwd; /* X, norm_weight, router as in the forward call (Q, R unused) */
+    const void *dQ;               /* bf16 gradient w.r.t. Q, logical [B,H,S,d_h] with element strides dq_stride (B,H,S) */
+    int64_t dq_stride[3];
+    const float *dR;              /* [B,H,S,E] contiguous */
+    void *dX;                     /* out, bf16, same layout as X */
+    float *d_router;              /* out, [H,d_h,E] */
+    float *d_norm_weight;         /* out, [H,d_h]; ignored when norm_weight is NULL */
+    void *workspace;              /* flashmhf_prologue_backward_workspace_bytes(), 256-byte aligned */
+    size_t workspace_bytes;
+} flashmhf_prologue_bwd_params;
+
+/* Replaces modeling_mhffnmoe.py:362-386 (forward) and its autograd (backward).  Enqueue and return. */
+int flashmhf_prologue_forward(const flashmhf_prologue_params *p, void *stream);
+size_t flashmhf_prologue_backward_workspace_bytes(const flashmhf_prologue_params *p);
+int flashmhf_prologue_backward(const flashmhf_prologue_bwd_params *p, void *stream);
 
 /* SYNCHRONOUS.  Waits for the current device, then reads and clears the status word the kernels
  * write when a bounded wait runs out.  *code = 0 if none did; otherwise a kernel/role identifier,
@@ -145,7 +181,7 @@ int flashmhf_device_status(int *code);
  * synchronisation, up to `max_marks` events in total).  flashmhf_profile_end is SYNCHRONOUS: it
  * waits for the device and returns, for each kernel launched in between, its duration in
  * milliseconds and a tag (1 forward, 2 backward dQ/dR, 3 backward dK/dU/dV, 4 backward split
- * reductions, 5 forward split reduction).
+ * reductions, 5 forward split reduction, 6 prologue forward, 7 prologue backward, 8 its reductions).
  * One profiling session at a time, calls from one stream.  Reference counterpart: none. */
 int flashmhf_profile_begin(int max_marks);
 int flashmhf_profile_end(float *ms, int *tags, int capacity, int *n_out);
