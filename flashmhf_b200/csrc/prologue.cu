@@ -15,11 +15,12 @@
 // time: lane l holds the d_h/32 consecutive elements d = l*d_h/32 .. (one 8-byte load per lane for
 // d_h = 128, so a row is one fully coalesced 256-byte request).  A block serves one head, so each lane
 // keeps its slice of that head's router matrix (and, in the backward, of its gradient) in registers
-// for the whole block; the per-row work is then a few dozen FMAs and shuffles.  Each warp walks its
-// rows two at a time with the next pair's loads issued before the current pair's arithmetic, which is
-// what hides the DRAM latency at one block per SM.  Weight gradients leave the block as per-block partial
-// sums and are added over blocks by a second kernel in a fixed order (no floating-point atomics, so
-// results are bit-reproducible).
+// for the whole block; the per-row work is then a few dozen FMAs and shuffles.  The grid is persistent
+// (heads x about one or two blocks per SM): a block loads its head's router matrix once, through shared
+// memory, and then its warps take row pairs round-robin until the tokens run out, the next pair's loads
+// issued before the current pair's arithmetic, which is what hides the DRAM latency at this occupancy.
+// Weight gradients leave the block as per-block partial sums and are added over blocks by a second
+// kernel in a fixed order (no floating-point atomics, so results are bit-reproducible).
 #include "kernels.h"
 #include "tc_common.cuh"
 
@@ -27,10 +28,15 @@ namespace fmhf {
 namespace {
 
 constexpr int kWarps = 8;             // warps per block
-constexpr int kRowsPerWarp = 32;      // token rows each warp walks through
-constexpr int kRowsPerBlock = kWarps * kRowsPerWarp;
 constexpr int kNR = 2;                // rows a warp has in flight
 constexpr int kMaxE = 32;
+constexpr int kNumSMs = 148;
+constexpr int kFwdBlocksPerSM = 2;
+
+// Row pair q of warp `warp` in block column `by` of `gy`: pairs are dealt round-robin over warps, then blocks.
+__device__ __forceinline__ long long first_row(int q, int by, int gy, int warp) {
+    return (long long)kNR * (((long long)q * gy + by) * kWarps + warp);
+}
 
 struct ProArgs {
     const __nv_bfloat16 *X;   // [B,S,H,Dh]
@@ -39,7 +45,13 @@ struct ProArgs {
     const float *router;      // [H,Dh,E]
     float eps;
     int T, H, E, S;           // T = B*S tokens
+    unsigned s_mul, s_shift;  // t / S == (t * s_mul) >> s_shift for 0 <= t < 2^31
 };
+
+// Division of a token index by the sequence length without the 64-bit divide: round-up multiplier.
+__device__ __forceinline__ int div_by_s(long long t, const ProArgs &a) {
+    return (int)(((unsigned long long)(unsigned)t * a.s_mul) >> a.s_shift);
+}
 
 template <int N>
 __device__ __forceinline__ float group_sum(float v) {  // sum over aligned groups of N lanes
@@ -114,21 +126,28 @@ struct RouterSlice {
     float reg[kRegs ? EPL : 1][kRegs ? EP : 1];
     const float *sm;
     int lane;
-    __device__ __forceinline__ void init(const float *router_h, float *smem, int E, int lane_) {
+    // Stages router[h] (Dh*E floats) in shared memory with coalesced loads; then either copies this lane's
+    // slice to registers or leaves it there re-ordered.  `stage` needs Dh*E floats (2*Dh*E when !kRegs).
+    __device__ __forceinline__ void init(const float *router_h, float *stage, int E, int lane_) {
         lane = lane_;
-        sm = smem;
+        const int n = EPL * 32 * E;
+        for (int k = threadIdx.x; k < n; k += blockDim.x) stage[k] = router_h[k];
+        __syncthreads();
         if constexpr (kRegs) {
+            sm = stage;
 #pragma unroll
             for (int i = 0; i < EPL; ++i)
 #pragma unroll
-                for (int e = 0; e < EP; ++e) reg[i][e] = e < E ? router_h[(lane * EPL + i) * E + e] : 0.f;
+                for (int e = 0; e < EP; ++e) reg[i][e] = e < E ? stage[(lane * EPL + i) * E + e] : 0.f;
         } else {
-            for (int k = threadIdx.x; k < EPL * 32 * E; k += blockDim.x) {
+            float *dst = stage + n;
+            for (int k = threadIdx.x; k < n; k += blockDim.x) {
                 const int d = k / E, e = k - d * E;  // d = l*EPL + i
-                smem[(e * EPL + d % EPL) * 32 + d / EPL] = router_h[k];
+                dst[(e * EPL + d % EPL) * 32 + d / EPL] = stage[k];
             }
-            __syncthreads();
+            sm = dst;
         }
+        __syncthreads();
     }
     __device__ __forceinline__ float at(int i, int e) const {
         if constexpr (kRegs) return reg[i][e];
@@ -170,7 +189,7 @@ __device__ __forceinline__ void row_forward(Row<DH / 32> &r, const float (&w)[DH
         part[e] = v;
     }
     const float logit = reduce_transpose<EP>(part, lane);
-    r.sg = (lane & (EP - 1)) < E ? 1.f / (1.f + expf(-logit)) : 0.f;
+    r.sg = (lane & (EP - 1)) < E ? __fdividef(1.f, 1.f + __expf(-logit)) : 0.f;
     r.D = fmaxf(group_sum<EP>(r.sg), 1e-20f);
 }
 
@@ -186,33 +205,32 @@ prologue_fwd_kernel(const ProArgs a, __nv_bfloat16 *Q, float *R) {
 #pragma unroll
     for (int i = 0; i < EPL; ++i) w[i] = NORM ? a.W[h * DH + lane * EPL + i] : 1.f;
 
-    const int t0 = blockIdx.y * kRowsPerBlock + warp * kRowsPerWarp;
+    const int by = blockIdx.y, gy = gridDim.y;
     float xn[kNR][EPL];
+    long long t = first_row(0, by, gy, warp);
 #pragma unroll
-    for (int k = 0; k < kNR; ++k)
-        load_row<EPL>(a.X + (long long)(t0 + k) * a.x_tok + h * DH, lane, t0 + k < a.T, xn[k]);
-    for (int j = 0; j < kRowsPerWarp; j += kNR) {
-        const int t = t0 + j;
-        if (t >= a.T) break;
+    for (int k = 0; k < kNR; ++k) load_row<EPL>(a.X + (t + k) * a.x_tok + h * DH, lane, t + k < a.T, xn[k]);
+    for (int q = 0; t < a.T; ++q) {
+        const long long tn = first_row(q + 1, by, gy, warp);
         Row<EPL> r[kNR];
 #pragma unroll
         for (int k = 0; k < kNR; ++k) {
 #pragma unroll
             for (int i = 0; i < EPL; ++i) r[k].x[i] = xn[k][i];
-            const int tn = t + kNR + k;
-            load_row<EPL>(a.X + (long long)tn * a.x_tok + h * DH, lane, j + kNR < kRowsPerWarp && tn < a.T, xn[k]);
+            load_row<EPL>(a.X + (tn + k) * a.x_tok + h * DH, lane, tn + k < a.T, xn[k]);
         }
 #pragma unroll
         for (int k = 0; k < kNR; ++k) row_forward<DH, EP, NORM>(r[k], w, rt, a.eps, a.E, lane);
 #pragma unroll
         for (int k = 0; k < kNR; ++k) {
-            const int tk = t + k;
+            const long long tk = t + k;
             if (tk < a.T) {
-                if (NORM) store_row<EPL>(Q + (long long)tk * a.x_tok + h * DH, lane, r[k].y);
-                const int b = tk / a.S, s = tk - b * a.S;
-                if (lane < a.E) R[(((long long)b * a.H + h) * a.S + s) * a.E + lane] = r[k].sg / r[k].D;
+                if (NORM) store_row<EPL>(Q + tk * a.x_tok + h * DH, lane, r[k].y);
+                const long long b = div_by_s(tk, a), s = tk - b * a.S;
+                if (lane < a.E) R[((b * a.H + h) * a.S + s) * a.E + lane] = __fdividef(r[k].sg, r[k].D);
             }
         }
+        t = tn;
     }
 }
 
@@ -231,9 +249,10 @@ prologue_bwd_kernel(const ProArgs a, const ProBwdArgs g) {
     constexpr int EPL = DH / 32;
     extern __shared__ float sm[];
     const int E = a.E, DE = DH * E;
-    // shared: [router slice when it is not in registers] [per-warp d router: kWarps*DE] [per-warp d w: kWarps*DH]
+    // shared: [router staging: DE, twice that when the slice stays in shared memory]
+    //         [per-warp d router: kWarps*DE] [per-warp d w: kWarps*DH]
     float *router_s = sm;
-    float *acc_r = sm + (RouterSlice<EPL, EP>::kRegs ? 0 : DE), *acc_w = acc_r + kWarps * DE;
+    float *acc_r = sm + (RouterSlice<EPL, EP>::kRegs ? DE : 2 * DE), *acc_w = acc_r + kWarps * DE;
     const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     RouterSlice<EPL, EP> rt;
     rt.init(a.router + (long long)h * DE, router_s, E, lane);
@@ -246,21 +265,21 @@ prologue_bwd_kernel(const ProArgs a, const ProBwdArgs g) {
         for (int e = 0; e < EP; ++e) racc[i][e] = 0.f;
     }
 
-    const int t0 = blockIdx.y * kRowsPerBlock + warp * kRowsPerWarp;
+    const int by = blockIdx.y, gy = gridDim.y;
     float xn[kNR][EPL], qn[kNR][EPL], gn[kNR];
-    auto prefetch = [&](int k, int t, bool ok) {
-        ok = ok && t < a.T;
-        const int b = ok ? t / a.S : 0, s = ok ? t - b * a.S : 0;
-        load_row<EPL>(a.X + (long long)t * a.x_tok + h * DH, lane, ok, xn[k]);
-        load_row<EPL>(g.dQ + (long long)b * g.dq_b + (long long)h * g.dq_h + (long long)s * g.dq_s, lane, ok, qn[k]);
-        gn[k] = ok && lane < E ? __ldg(g.dR + (((long long)b * a.H + h) * a.S + s) * E + lane) : 0.f;
+    auto prefetch = [&](int k, long long tt) {
+        const bool ok = tt < a.T;
+        const long long b = ok ? div_by_s(tt, a) : 0, s = ok ? tt - b * a.S : 0;
+        load_row<EPL>(a.X + tt * a.x_tok + h * DH, lane, ok, xn[k]);
+        load_row<EPL>(g.dQ + b * g.dq_b + (long long)h * g.dq_h + s * g.dq_s, lane, ok, qn[k]);
+        gn[k] = ok && lane < E ? __ldg(g.dR + ((b * a.H + h) * a.S + s) * E + lane) : 0.f;
     };
+    long long t = first_row(0, by, gy, warp);
 #pragma unroll
-    for (int k = 0; k < kNR; ++k) prefetch(k, t0 + k, true);
+    for (int k = 0; k < kNR; ++k) prefetch(k, t + k);
 
-    for (int j = 0; j < kRowsPerWarp; j += kNR) {
-        const int t = t0 + j;
-        if (t >= a.T) break;
+    for (int q = 0; t < a.T; ++q) {
+        const long long tn = first_row(q + 1, by, gy, warp);
         Row<EPL> r[kNR];
         float dy[kNR][EPL], ge[kNR];
 #pragma unroll
@@ -268,7 +287,7 @@ prologue_bwd_kernel(const ProArgs a, const ProBwdArgs g) {
 #pragma unroll
             for (int i = 0; i < EPL; ++i) { r[k].x[i] = xn[k][i]; dy[k][i] = qn[k][i]; }
             ge[k] = gn[k];
-            prefetch(k, t + kNR + k, j + kNR < kRowsPerWarp);
+            prefetch(k, tn + k);
         }
 #pragma unroll
         for (int k = 0; k < kNR; ++k) row_forward<DH, EP, NORM>(r[k], w, rt, a.eps, E, lane);
@@ -276,7 +295,7 @@ prologue_bwd_kernel(const ProArgs a, const ProBwdArgs g) {
         for (int k = 0; k < kNR; ++k) {
             // R_e = sg_e / D  ->  d sg_e = (g_e - sum_k g_k R_k) / D ;  d logit_e = d sg_e * sg_e * (1 - sg_e).
             // A clamped denominator (D = 1e-20) has no gradient through the sum, as torch's clamp.
-            const float inv = 1.f / r[k].D;
+            const float inv = __fdividef(1.f, r[k].D);
             const float gR = r[k].D > 1e-20f ? group_sum<EP>(ge[k] * r[k].sg * inv) : 0.f;
             const float dl = (ge[k] - gR) * inv * r[k].sg * (1.f - r[k].sg);   // 0 for lanes beyond E (sg = 0)
             // dy = dQ + router . dlogits ;  d router += y (x) dlogits
@@ -308,8 +327,9 @@ prologue_bwd_kernel(const ProArgs a, const ProBwdArgs g) {
 #pragma unroll
                 for (int i = 0; i < EPL; ++i) dx[i] = dy[k][i];
             }
-            if (t + k < a.T) store_row<EPL>(g.dX + (long long)(t + k) * a.x_tok + h * DH, lane, dx);
+            if (t + k < a.T) store_row<EPL>(g.dX + (t + k) * a.x_tok + h * DH, lane, dx);
         }
+        t = tn;
     }
     // warps' accumulators -> shared -> this block's partial sums (fixed order)
     float *my_r = acc_r + warp * DE, *my_w = acc_w + warp * DH;
@@ -356,7 +376,7 @@ __global__ void __launch_bounds__(128) prologue_reduce_kernel(const float *part,
 int check_pro(const flashmhf_prologue_params &p) {
     if (p.B < 1 || p.S < 1 || p.H < 1 || p.E < 1 || p.E > kMaxE) return FLASHMHF_ERR_BAD_SHAPE;
     if (p.Dh != 64 && p.Dh != 96 && p.Dh != 128) return FLASHMHF_ERR_BAD_SHAPE;
-    if ((long long)p.B * p.S > 0x7fffffffLL - 2 * kRowsPerBlock) return FLASHMHF_ERR_BAD_SHAPE;
+    if ((long long)p.B * p.S > 0x7fffffffLL) return FLASHMHF_ERR_BAD_SHAPE;
     if (!p.X || !p.router || !p.R) return FLASHMHF_ERR_NULL;
     if (p.norm_weight && !p.Q) return FLASHMHF_ERR_NULL;
     if (p.x_token_stride < (int64_t)p.H * p.Dh || (p.x_token_stride & 7)) return FLASHMHF_ERR_BAD_STRIDE;
@@ -365,12 +385,21 @@ int check_pro(const flashmhf_prologue_params &p) {
     return FLASHMHF_OK;
 }
 ProArgs pro_args(const flashmhf_prologue_params &p) {
+    // l = ceil(log2 S); m = floor(2^(31+l) / S) + 1 < 2^32 gives exact quotients for dividends below 2^31
+    unsigned l = 0;
+    while ((1ull << l) < (unsigned long long)p.S) ++l;
+    const unsigned mul = (unsigned)(((1ull << (31 + l)) / (unsigned long long)p.S) + 1ull);
     return ProArgs{static_cast<const __nv_bfloat16 *>(p.X), p.x_token_stride, p.norm_weight, p.router, p.eps,
-                   p.B * p.S, p.H, p.E, p.S};
+                   p.B * p.S, p.H, p.E, p.S, mul, 31 + l};
 }
-int tiles(const flashmhf_prologue_params &p) { return (p.B * p.S + kRowsPerBlock - 1) / kRowsPerBlock; }
+// Blocks per head: enough to fill the GPU `per_sm` times over, never more than there are row pairs to deal.
+int blocks_per_head(const flashmhf_prologue_params &p, int per_sm) {
+    const long long pairs = ((long long)p.B * p.S + kNR - 1) / kNR, most = (pairs + kWarps - 1) / kWarps;
+    const long long want = kNumSMs * per_sm / p.H > 1 ? kNumSMs * per_sm / p.H : 1;
+    return (int)(want < most ? want : most);
+}
 
-size_t fwd_smem(int DH, int EP, int E) { return EP <= 16 ? 0 : (size_t)DH * E * sizeof(float); }
+size_t fwd_smem(int DH, int EP, int E) { return (size_t)(EP <= 16 ? 1 : 2) * DH * E * sizeof(float); }
 size_t bwd_smem(int DH, int EP, int E) {
     return fwd_smem(DH, EP, E) + (size_t)kWarps * ((size_t)DH * E + DH) * sizeof(float);
 }
@@ -378,6 +407,8 @@ size_t bwd_smem(int DH, int EP, int E) {
 template <int DH, int EP, bool NORM>
 cudaError_t launch_fwd(const ProArgs &a, dim3 grid, __nv_bfloat16 *Q, float *R, cudaStream_t st) {
     const size_t smem = fwd_smem(DH, EP, a.E);
+    cudaError_t e = cudaFuncSetAttribute(prologue_fwd_kernel<DH, EP, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
     prologue_fwd_kernel<DH, EP, NORM><<<grid, kWarps * 32, smem, st>>>(a, Q, R);
     return cudaGetLastError();
 }
@@ -412,7 +443,7 @@ int prologue_forward(const flashmhf_prologue_params &p, cudaStream_t st, int *n_
     int rc = check_pro(p);
     if (rc) return rc;
     const ProArgs a = pro_args(p);
-    const dim3 grid(p.H, tiles(p));
+    const dim3 grid(p.H, blocks_per_head(p, kFwdBlocksPerSM));
     __nv_bfloat16 *Q = static_cast<__nv_bfloat16 *>(p.Q);
     cudaError_t e = cudaSuccess;
     prof_mark(st, kMarkStart);
@@ -426,7 +457,7 @@ int prologue_forward(const flashmhf_prologue_params &p, cudaStream_t st, int *n_
 }
 
 size_t prologue_backward_workspace_bytes(const flashmhf_prologue_params &p) {
-    return (size_t)tiles(p) * p.H * ((size_t)p.Dh * p.E + p.Dh) * sizeof(float);
+    return (size_t)blocks_per_head(p, 1) * p.H * ((size_t)p.Dh * p.E + p.Dh) * sizeof(float);
 }
 
 int prologue_backward(const flashmhf_prologue_bwd_params &q, cudaStream_t st, int *n_launch) {
@@ -441,7 +472,7 @@ int prologue_backward(const flashmhf_prologue_bwd_params &q, cudaStream_t st, in
     if (!q.workspace || q.workspace_bytes < need || (reinterpret_cast<uintptr_t>(q.workspace) & 255u))
         return FLASHMHF_ERR_WORKSPACE;
     const ProArgs a = pro_args(p);
-    const int ny = tiles(p), DE = p.Dh * p.E;
+    const int ny = blocks_per_head(p, 1), DE = p.Dh * p.E;
     float *part_r = static_cast<float *>(q.workspace);
     float *part_w = part_r + (size_t)ny * p.H * DE;
     const ProBwdArgs g{static_cast<const __nv_bfloat16 *>(q.dQ), q.dq_stride[0], q.dq_stride[1], q.dq_stride[2], q.dR,
