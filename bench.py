@@ -168,6 +168,50 @@ def run_reference(args, rank, world):
     }))
 
 
+def lm_train_370m(args, rank, world, dev, sync_all):
+    """The second half of the headline metric: full training steps (forward, backward, gradient all-reduce,
+    AdamW) of the 370M decoder LM at batch 16 x 2048 per GPU, bf16, uniform random token ids, data-parallel.
+    Token ids come from pinned host memory every step and the loss is read back to the host, inside the timed region."""
+    from flashmhf_b200 import _lib, dp, lm
+    cfg = lm.LMConfig.lm_370m()
+    Bt, St = 16, 2048
+    model = lm.DecoderLM(cfg).init_weights(seed=0).to(dev).to(torch.bfloat16)   # same seed -> same weights on every rank
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+    red = dp.GradReducer(buckets=dp.lm_buckets(model)) if world > 1 else None
+    ids_host = torch.randint(0, cfg.vocab_size, (Bt, St), generator=torch.Generator().manual_seed(rank)).pin_memory()
+    loss_host = torch.zeros((), dtype=torch.float32).pin_memory()
+
+    def step():
+        ids = ids_host.to(dev, non_blocking=True)
+        loss = lm.train_step(model, opt, ids, red)
+        loss_host.copy_(loss, non_blocking=True)
+
+    for _ in range(3):
+        step()
+    sync_all()
+    first_loss = float(loss_host)
+    launches0 = _lib.launch_count()
+    _lib.profile_begin(16 * cfg.num_hidden_layers * args.lm_steps + 16)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.lm_steps):
+        step()
+    e1.record()
+    sync_all()
+    kernel_ms = _lib.profile_end(capacity=16 * cfg.num_hidden_layers * args.lm_steps + 16)
+    ms = dp.max_over_ranks(e0.elapsed_time(e1) / args.lm_steps, dev)
+    ours_ms = sum(sum(v) for v in kernel_ms.values()) / args.lm_steps
+    flops = lm.train_flops_per_token(cfg, St) * Bt * St
+    return {"tokens_per_s": Bt * St * world / (ms * 1e-3), "ms_per_step": ms, "steps": args.lm_steps, "warmup": 3,
+            "batch_per_gpu": Bt, "seq_len": St, "n_params": lm.param_count(model), "optimizer": "AdamW (torch fused), bf16 parameters",
+            "model_tflops_per_gpu": flops / (ms * 1e-3) / 1e12,
+            "ffn_kernels_ms_per_step": ours_ms, "ffn_kernels_share": ours_ms / ms,
+            "ffn_kernel_launches_per_step": (_lib.launch_count() - launches0) / args.lm_steps,
+            "loss_first_last": [first_loss, float(loss_host)],
+            "outside_the_ffn": "attention = torch scaled_dot_product_attention, projections = cuBLAS, loss = torch cross_entropy",
+            "parallelism": f"dp{world}" + (" + per-layer NCCL all-reduce overlapped with backward" if world > 1 else "")}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -176,6 +220,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="B=2 instead of 16 (for profiler captures)")
+    ap.add_argument("--no-lm", action="store_true", help="skip the 370M LM training-step measurement")
+    ap.add_argument("--lm-steps", type=int, default=8)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -278,6 +324,12 @@ def main():
     value = fl / (ms * 1e-3) / 1e12
     e2e_value = fl / (e2e_ms * 1e-3) / 1e12
 
+    train = None
+    if not args.no_lm and not args.small:
+        del res, outs_host, hQ, hdO, hR
+        torch.cuda.empty_cache()
+        train = lm_train_370m(args, rank, world, dev, sync_all)
+
     if rank == 0:
         peaks = measured_peaks()
         per_kernel = {k: statistics.mean(v) for k, v in kernel_ms.items()}
@@ -305,6 +357,9 @@ def main():
             "clocks": clocks,
             "roofline": roof,
         }
+        if train is not None:
+            train["mfu_of_measured_sustained"] = train["model_tflops_per_gpu"] / peaks["sustained"]
+            out["train_370m"] = train
         if not args.no_cpu_baseline and world == 1:
             out["cpu_baseline"] = cpu_baseline(w)
         print(json.dumps(out))

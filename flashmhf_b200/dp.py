@@ -50,3 +50,82 @@ def max_over_ranks(value, device, group=None):
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     return float(t.item())
+
+
+class GradReducer:
+    """Data-parallel gradient exchange overlapped with the backward pass.
+
+    Parameters are grouped into buckets (one per decoder layer for the LM in flashmhf_b200/lm.py: pass
+    ``buckets`` as lists of parameters, else one bucket per ``bucket_bytes`` in reverse order).  When the
+    last gradient of a bucket has been accumulated, its gradients are packed into one flat tensor,
+    pre-divided by the world size and all-reduced asynchronously, so the exchange of layer l runs
+    while the backward of layer l-1 computes.  ``finish()`` waits for all buckets and copies the means
+    back into ``p.grad``; call it before the optimizer step.  With one rank it does nothing."""
+
+    def __init__(self, params=None, buckets=None, bucket_bytes=64 << 20, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+        self._pending, self._hooks = [], []
+        if buckets is None:
+            buckets, cur, size = [], [], 0
+            for p in reversed([p for p in params if p.requires_grad]):
+                cur.append(p)
+                size += p.numel() * p.element_size()
+                if size >= bucket_bytes:
+                    buckets.append(cur)
+                    cur, size = [], 0
+            if cur:
+                buckets.append(cur)
+        self.buckets = [[p for p in b if p.requires_grad] for b in buckets]
+        self.buckets = [b for b in self.buckets if b]
+        self._left = [len(b) for b in self.buckets]
+        if self.world > 1:
+            for i, b in enumerate(self.buckets):
+                for p in b:
+                    self._hooks.append(p.register_post_accumulate_grad_hook(lambda _p, i=i: self._ready(i)))
+
+    def _ready(self, i):
+        self._left[i] -= 1
+        if self._left[i] == 0:
+            self._launch(i)
+
+    def _launch(self, i):
+        ps = self.buckets[i]
+        flat = torch.cat([p.grad.reshape(-1) for p in ps])
+        flat /= self.world
+        work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        self._pending.append((work, flat, ps))
+
+    def finish(self):
+        if self.world == 1:
+            return
+        for i, n in enumerate(self._left):       # buckets whose parameters did not all receive a gradient this step
+            if n != 0 and n != len(self.buckets[i]):
+                raise RuntimeError("a gradient bucket was only partly filled; pass buckets that match the graph")
+        for work, flat, ps in self._pending:
+            work.wait()
+            off = 0
+            for p in ps:
+                n = p.numel()
+                p.grad.copy_(flat[off:off + n].view_as(p.grad))
+                off += n
+        self._pending.clear()
+        self._left = [len(b) for b in self.buckets]
+
+    def remove(self):
+        for h in self._hooks:
+            h.remove()
+        self._hooks.clear()
+
+
+def lm_buckets(model):
+    """One bucket per decoder layer (in backward order), one for the head and final norm, one for the embedding."""
+    layers = [list(l.parameters()) for l in model.model.layers]
+    seen, out = set(), []
+    head = [model.lm_head.weight] + list(model.model.norm.parameters())
+    for group in [head] + layers[::-1] + [[model.model.embed_tokens.weight]]:
+        g = [p for p in group if id(p) not in seen]
+        seen.update(id(p) for p in g)
+        if g:
+            out.append(g)
+    return out

@@ -1,0 +1,228 @@
+"""A minimal decoder LM around the FFN layer, for whole-model measurements and layer-in-context tests.
+
+The architecture and every parameter name follow the reference model
+(models/flashmhf/modeling_mhffnmoe.py: decoder layer :601-652, attention :523-598, RMSNorm :73-90,
+rotary tables :164-175, FFN layer :256-431, model :784-921, LM head :1055-1090), so a reference
+state dict loads with ``load_state_dict``.  Only the FFN layer is this package's own code (the fused
+prologue + the CUDA operator); attention, norms, embeddings and the loss are plain PyTorch calls: they are
+the surroundings the operator is measured in, not part of it.
+
+``ffn`` lets a caller substitute the FFN layer function; the default is the CUDA layer and there is
+no CPU stand-in for it in this package.
+"""
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+@dataclass
+class LMConfig:
+    """Field meanings as in the reference's configuration files (configs/mhffnmoe/*.json)."""
+    vocab_size: int = 50280
+    hidden_size: int = 1024
+    num_hidden_layers: int = 20
+    num_attention_heads: int = 16
+    num_key_value_heads: int = 16
+    intermediate_size: int = 2816          # per-head intermediate width I = E * d_e
+    mhffnmoe_num_heads: int = 8
+    mhffnmoe_num_kuv_heads: int = 8
+    mhffnmoe_num_experts: int = 11
+    mhffnmoe_apply_rmsnorm: bool = True
+    mhffnmoe_skip_linear: bool = False
+    rms_norm_eps: float = 1e-5
+    rope_theta: float = 10000.0
+    tie_word_embeddings: bool = False
+
+    @staticmethod
+    def lm_370m():
+        """configs/mhffnmoe/configure-2-mhffnmoe-TriDao-350M.json with the 50280-entry vocabulary."""
+        return LMConfig()
+
+    @staticmethod
+    def lm_128m():
+        """configs/mhffnmoe/configure-1-tinymhffnmoe.json: hidden 768, 10 layers, 8 FFN heads of 96, 8 x 256."""
+        return LMConfig(hidden_size=768, num_hidden_layers=10, num_attention_heads=12, num_key_value_heads=12,
+                        intermediate_size=2048, mhffnmoe_num_heads=8, mhffnmoe_num_kuv_heads=8, mhffnmoe_num_experts=8,
+                        mhffnmoe_apply_rmsnorm=False, tie_word_embeddings=True)
+
+    @staticmethod
+    def lm_1p3b():
+        """configs/mhffnmoe/configure-3-mhffnmoe-TriDao-1.3B.json."""
+        return LMConfig(hidden_size=2048, num_hidden_layers=20, num_attention_heads=32, num_key_value_heads=32,
+                        intermediate_size=5632, mhffnmoe_num_heads=16, mhffnmoe_num_kuv_heads=16, mhffnmoe_num_experts=22)
+
+
+class RMSNorm(nn.Module):
+    """fp32 statistics, weight applied after the cast back (modeling_mhffnmoe.py:82-87)."""
+
+    def __init__(self, n, eps):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(n))
+        self.eps = eps
+
+    def forward(self, x):
+        dt = x.dtype
+        x = x.float()
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps)
+        return self.weight * x.to(dt)
+
+
+def rotary_tables(S, head_dim, theta, device, dtype):
+    """cos/sin [S, head_dim] as the reference builds them (fp32 angles, duplicated halves, cast to the activations' dtype)."""
+    inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.int64, device=device).float() / head_dim))
+    ang = torch.arange(S, device=device).float()[:, None] * inv_freq[None, :]
+    emb = torch.cat((ang, ang), dim=-1)
+    return emb.cos().to(dtype), emb.sin().to(dtype)
+
+
+def _rotate_half(x):
+    h = x.shape[-1] // 2
+    return torch.cat((-x[..., h:], x[..., :h]), dim=-1)
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg):
+        super().__init__()
+        self.nh, self.nkv = cfg.num_attention_heads, cfg.num_key_value_heads
+        self.hd = cfg.hidden_size // cfg.num_attention_heads
+        self.q_proj = nn.Linear(cfg.hidden_size, self.nh * self.hd, bias=False)
+        self.k_proj = nn.Linear(cfg.hidden_size, self.nkv * self.hd, bias=False)
+        self.v_proj = nn.Linear(cfg.hidden_size, self.nkv * self.hd, bias=False)
+        self.o_proj = nn.Linear(self.nh * self.hd, cfg.hidden_size, bias=False)
+
+    def forward(self, x, cos, sin):
+        B, S, _ = x.shape
+        q = self.q_proj(x).view(B, S, self.nh, self.hd).transpose(1, 2)
+        k = self.k_proj(x).view(B, S, self.nkv, self.hd).transpose(1, 2)
+        v = self.v_proj(x).view(B, S, self.nkv, self.hd).transpose(1, 2)
+        q = q * cos + _rotate_half(q) * sin
+        k = k * cos + _rotate_half(k) * sin
+        o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.nkv != self.nh)
+        return self.o_proj(o.transpose(1, 2).reshape(B, S, self.nh * self.hd))
+
+
+class _HeadNorm(nn.Module):
+    def __init__(self, H, dh):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(H, dh))
+
+
+class MHFFN(nn.Module):
+    """The reference's FFN layer (modeling_mhffnmoe.py:256-431) with its parameter names; the arithmetic is ``ffn``."""
+
+    def __init__(self, cfg, ffn):
+        super().__init__()
+        self.cfg, self.ffn = cfg, ffn
+        H, Hk, hid, I = cfg.mhffnmoe_num_heads, cfg.mhffnmoe_num_kuv_heads, cfg.hidden_size, cfg.intermediate_size
+        dh = hid // H
+        if not cfg.mhffnmoe_skip_linear:
+            self.w_self = nn.Linear(hid, hid, bias=False)
+            self.w_self_2 = nn.Linear(hid, hid, bias=False)
+        else:
+            self.w_self = self.w_self_2 = None
+        self.gate_weight = nn.Parameter(torch.empty(I, dh * Hk))
+        self.up_weight = nn.Parameter(torch.empty(I, dh * Hk))
+        self.down_weight = nn.Parameter(torch.empty(I, dh * Hk))
+        self.router = nn.Parameter(torch.empty(H, dh, cfg.mhffnmoe_num_experts))
+        self.q_norm = _HeadNorm(H, dh)
+
+    def forward(self, x):
+        c = self.cfg
+        p = {"w_self": None if self.w_self is None else self.w_self.weight,
+             "w_self_2": None if self.w_self_2 is None else self.w_self_2.weight,
+             "gate_weight": self.gate_weight, "up_weight": self.up_weight, "down_weight": self.down_weight,
+             "router": self.router, "q_norm": self.q_norm.weight}
+        return self.ffn(x, p, H=c.mhffnmoe_num_heads, Hkuv=c.mhffnmoe_num_kuv_heads, E=c.mhffnmoe_num_experts,
+                        apply_rmsnorm=c.mhffnmoe_apply_rmsnorm, eps=c.rms_norm_eps)
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg, ffn):
+        super().__init__()
+        self.self_attn = Attention(cfg)
+        self.mlp = MHFFN(cfg, ffn)
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+
+    def forward(self, h, cos, sin):
+        h = h + self.self_attn(self.input_layernorm(h), cos, sin)
+        return h + self.mlp(self.post_attention_layernorm(h))
+
+
+class _Body(nn.Module):
+    def __init__(self, cfg, ffn):
+        super().__init__()
+        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
+        self.layers = nn.ModuleList(DecoderLayer(cfg, ffn) for _ in range(cfg.num_hidden_layers))
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+
+
+class DecoderLM(nn.Module):
+    """ids [B,S] -> logits [B,S,vocab]; ``loss`` is the next-token cross entropy the reference trains with
+    (labels = ids shifted by one, mean over B*(S-1) positions, computed in fp32)."""
+
+    def __init__(self, cfg, ffn=None):
+        super().__init__()
+        if ffn is None:
+            from .layer import mhffn_layer as ffn  # the CUDA layer; raises at call time without the library or a GPU
+        self.cfg = cfg
+        self.model = _Body(cfg, ffn)
+        self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
+        if cfg.tie_word_embeddings:
+            self.lm_head.weight = self.model.embed_tokens.weight
+
+    @torch.no_grad()
+    def init_weights(self, seed=0, std=0.02):
+        """Every matrix ~ N(0, std) from one seeded CPU generator in sorted-name order; norm weights stay 1."""
+        g = torch.Generator().manual_seed(seed)
+        for name, p in sorted(self.named_parameters()):
+            if name.endswith("norm.weight") or name.endswith("layernorm.weight"):
+                p.fill_(1.0)
+            else:
+                p.copy_((torch.randn(p.shape, generator=g) * std).to(p.dtype))
+        return self
+
+    def hidden(self, ids):
+        B, S = ids.shape
+        h = self.model.embed_tokens(ids)
+        hd = self.cfg.hidden_size // self.cfg.num_attention_heads
+        cos, sin = rotary_tables(S, hd, self.cfg.rope_theta, ids.device, h.dtype)
+        for layer in self.model.layers:
+            h = layer(h, cos, sin)
+        return self.model.norm(h)
+
+    def forward(self, ids):
+        return self.lm_head(self.hidden(ids))
+
+    def loss(self, ids):
+        logits = self.forward(ids)
+        V = logits.shape[-1]
+        return F.cross_entropy(logits[:, :-1].float().reshape(-1, V), ids[:, 1:].reshape(-1))
+
+
+def train_step(model, opt, ids, reducer=None):
+    """One full training step: forward, backward, gradient exchange (``reducer``: dp.GradReducer or None), AdamW."""
+    opt.zero_grad(set_to_none=True)
+    loss = model.loss(ids)
+    loss.backward()
+    if reducer is not None:
+        reducer.finish()
+    opt.step()
+    return loss.detach()
+
+
+def param_count(model):
+    return sum(p.numel() for p in model.parameters())
+
+
+def train_flops_per_token(cfg, S):
+    """6 x (matrix parameters touched per token) + causal attention (12 * L * hidden * S / 2), for MFU lines."""
+    hid, L, V = cfg.hidden_size, cfg.num_hidden_layers, cfg.vocab_size
+    hd = hid // cfg.num_attention_heads
+    attn = hid * hd * (2 * cfg.num_attention_heads + 2 * cfg.num_key_value_heads)
+    dh = hid // cfg.mhffnmoe_num_heads
+    ffn = (0 if cfg.mhffnmoe_skip_linear else 2 * hid * hid) + 3 * cfg.mhffnmoe_num_heads * cfg.intermediate_size * dh
+    return 6 * (L * (attn + ffn) + V * hid) + 6 * L * hid * S

@@ -48,7 +48,7 @@ def mhffn_forward(Q, K, U, V, R, *, out_dtype=None):
     g = H // hk
     K, U, V = repeat_kuv(K, g), repeat_kuv(U, g), repeat_kuv(V, g)
     acc_dtype = torch.float64 if Q.dtype == torch.float64 else torch.float32
-    out = torch.zeros(Q.shape, dtype=acc_dtype)
+    out = torch.zeros(Q.shape, dtype=acc_dtype, device=Q.device)
     for e in range(E):
         w = F.silu(Q @ K[:, e].transpose(1, 2))
         w = w * (Q @ U[:, e].transpose(1, 2))
@@ -71,7 +71,7 @@ def mhffn_backward(Q, K, U, V, R, dO):
     Kr, Ur, Vr = repeat_kuv(K, g), repeat_kuv(U, g), repeat_kuv(V, g)
     dQ = torch.zeros_like(Q)
     dKr, dUr, dVr = torch.zeros_like(Kr), torch.zeros_like(Ur), torch.zeros_like(Vr)
-    dR = torch.zeros(R.shape, dtype=Q.dtype)
+    dR = torch.zeros(R.shape, dtype=Q.dtype, device=Q.device)
     for e in range(E):
         r = R[..., e:e + 1].to(Q.dtype)
         M = Q @ Kr[:, e].transpose(1, 2)
