@@ -15,7 +15,9 @@
 // bwd_dw_kernel  -- weight-stationary.  One CTA owns one 64-row block of K, U and V of one K/U/V
 //   head and a contiguous range of token tiles (the token axis is split `nsplit` ways to fill the
 //   machine).  Weights stay in shared memory, {Q, dO} tiles stream through a ring of 2.
-//   Tensor memory: [dK;dU] accumulator (128 lanes), dV accumulator (M = 64), S, dA.
+//   Tensor memory: [dK;dU] accumulator (128 lanes), dV accumulator (transposed, d_h x 64, when d_h = 128; else
+//   M = 64), two S buffers and one dA buffer (the element-wise warps copy dA to registers first and hand it
+//   back at once), so that the recompute of tile i+1 runs under the element-wise math of tile i.
 //   Each CTA writes fp32 partial sums to the workspace; dw_reduce_kernel adds the splits in a fixed
 //   order and writes bf16 dK, dU, dV.
 //
@@ -398,8 +400,10 @@ struct DwSmem {
 // The Q half and the dO half of a token stage, and the [dM|dN] tile and the A tile, have barriers of their
 // own: each is needed by, and released after, a different MMA chain, and every cycle by which the next
 // load or the next MMA can start earlier shortens the loop load -> recompute -> element-wise -> accumulate.
-enum { DW_WFULL = 0, DW_QFULL = 1, DW_GFULL = 3, DW_QEMPTY = 5, DW_GEMPTY = 7, DW_SFULL = 9, DW_SEMPTY = 10,
-       DW_PFULL = 11, DW_AFULL = 12, DW_PEMPTY = 13, DW_AEMPTY = 14, DW_ACCFULL = 15, DW_BARS = 16 };
+// S has two buffers in tensor memory, each with its own full/empty pair, so that every waiter sees every
+// phase of the barrier it waits on (a one-bit parity cannot tell phase k from phase k+2).
+enum { DW_WFULL = 0, DW_QFULL = 1, DW_GFULL = 3, DW_QEMPTY = 5, DW_GEMPTY = 7, DW_SFULL = 9, DW_SEMPTY = 11,
+       DW_PFULL = 13, DW_AFULL = 14, DW_PEMPTY = 15, DW_AEMPTY = 16, DW_ACCFULL = 17, DW_DAEMPTY = 18, DW_BARS = 19 };
 
 struct DwArgs {
     const float *R;
@@ -434,7 +438,13 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int ntiles = tile_end - tile_begin;  // >= 1 by construction of the grid
     const WaitCtl ctl{abort_flag, args.status};
     constexpr int W = kKernelBwdDw * 100;
-    constexpr uint32_t kColKU = 0, kColV = 128, kColS = 256, kColdA = 384;
+    // dV^T = sum_t dO^T A (d_h x 64, M = 128, N = 64) needs half the columns and three quarters of the tensor-pipe
+    // time of dV = sum_t A^T dO (M = 64 runs at the M = 128 rate); it needs M = d_h = 128.
+    constexpr bool kVt = DH == 128;
+    // Columns: [dK;dU] at 0 (d_h wide), dV at 128 (64 wide transposed, else d_h wide), S buffers at 256 and 384, dA in
+    // the gap at 192.  d_h = 96 leaves no gap (dV reaches column 224): it keeps one S buffer, with dA at 384.
+    constexpr int kSB = DH == 96 ? 1 : 2;
+    constexpr uint32_t kColKU = 0, kColV = 128, kColS = 256, kColdA = kSB == 2 ? 192 : 384;
 
     auto tile_coords = [&](int i, int &ts, int &hh, int &bb) {  // token tile i of this CTA -> (seq tile, head, batch)
         const int ti = tile_begin + i;
@@ -453,8 +463,11 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             mbar_init(bar(DW_QEMPTY + s), 1);
             mbar_init(bar(DW_GEMPTY + s), 1);
         }
-        mbar_init(bar(DW_SFULL), 1);
-        mbar_init(bar(DW_SEMPTY), kActThreads);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar(DW_SFULL + b), 1);
+            mbar_init(bar(DW_SEMPTY + b), kActThreads);
+        }
+        mbar_init(bar(DW_DAEMPTY), kActThreads);
         mbar_init(bar(DW_PFULL), kActThreads);
         mbar_init(bar(DW_AFULL), kActThreads);
         mbar_init(bar(DW_PEMPTY), 1);
@@ -522,17 +535,20 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 FMHF_TRW(1, i, 0);
                 if (!mbar_wait(bar(DW_QFULL + st), ph, ctl, W + 4)) break;
                 FMHF_TRW(1, i, 1);
-                if (!mbar_wait(bar(DW_SEMPTY), (i & 1) ^ 1, ctl, W + 5)) break;
+                const int sb = i % kSB;
+                const uint32_t sph = (uint32_t)(i / kSB) & 1u;
+                if (!mbar_wait(bar(DW_SEMPTY + sb), sph ^ 1, ctl, W + 5)) break;
                 FMHF_TRW(1, i, 2);
                 tc_fence_after();
                 const uint64_t dq = dQk0 + st * kTokStep, dg = dGk0 + st * kTokStep;
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const int c = k >> 2, kk = k & 3;
-                    umma_ss(tmem + kColS, dq + ((c * kTile + kk * 32) >> 4), dKU + ((c * 2 * kWChunk + kk * 32) >> 4), idS,
-                            k > 0 ? 1u : 0u);
+                    umma_ss(tmem + kColS + sb * 2 * kBI, dq + ((c * kTile + kk * 32) >> 4),
+                            dKU + ((c * 2 * kWChunk + kk * 32) >> 4), idS, k > 0 ? 1u : 0u);
                 }
                 if (!mbar_wait(bar(DW_GFULL + st), ph, ctl, W + 4)) break;
+                if (!mbar_wait(bar(DW_DAEMPTY), (i & 1) ^ 1, ctl, W + 10)) break;
                 tc_fence_after();
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
@@ -540,7 +556,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     umma_ss(tmem + kColdA, dg + ((c * kTile + kk * 32) >> 4), dV + ((c * kWChunk + kk * 32) >> 4), idA,
                             k > 0 ? 1u : 0u);
                 }
-                umma_commit(bar(DW_SFULL));
+                umma_commit(bar(DW_SFULL + sb));
                 FMHF_TRW(1, i, 3);
                 if (++st == L::kTokStages) { st = 0; ph ^= 1; }
             }
@@ -549,7 +565,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         // MMA issuer 2: the accumulation chain [dK;dU] += [dM|dN]^T Q, dV += A^T dO.
         if (lane == 0) {
             constexpr uint32_t idKU = umma_idesc(128, DH, true, true);
-            constexpr uint32_t idV = umma_idesc(64, DH, true, true);
+            constexpr uint32_t idV = kVt ? umma_idesc(128, kBI, true, true) : umma_idesc(64, DH, true, true);
             const uint64_t dQmn0 = desc_mnmajor(sTok, kTile), dGmn0 = desc_mnmajor(sTok + L::kChunks * kTile, kTile),
                            dPmn = desc_mnmajor(sP, kTile), dAmn = desc_mnmajor(sA, kTile);
             constexpr uint64_t kTokStep = L::kTokStage >> 4;
@@ -569,8 +585,10 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 if (!mbar_wait(bar(DW_AFULL), i & 1, ctl, W + 6)) { ok = false; break; }
                 tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < kBT / 16; ++k)
-                    umma_ss(tmem + kColV, dAmn + k * 128, dg + k * 128, idV, (i > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < kBT / 16; ++k) {
+                    if (kVt) umma_ss(tmem + kColV, dg + k * 128, dAmn + k * 128, idV, (i > 0 || k > 0) ? 1u : 0u);
+                    else umma_ss(tmem + kColV, dAmn + k * 128, dg + k * 128, idV, (i > 0 || k > 0) ? 1u : 0u);
+                }
                 umma_commit(bar(DW_GEMPTY + st));  // dO of this stage and the A tile are free
                 umma_commit(bar(DW_AEMPTY));
                 FMHF_TRW(1, i, 6);
@@ -601,27 +619,34 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                                               (long long)t * args.r_ss + e) : 0.f;
             }
             FMHF_TRW(2 + half, i, 0);
-            if (!mbar_wait(bar(DW_SFULL), i & 1, ctl, W + 7)) { ok = false; break; }
+            const int sb = i % kSB;
+            if (!mbar_wait(bar(DW_SFULL + sb), (uint32_t)(i / kSB) & 1u, ctl, W + 7)) { ok = false; break; }
             FMHF_TRW(2 + half, i, 1);
             tc_fence_after();
-            uint32_t pm[16], pn[16], pa[16];
+            uint32_t pm[16], pn[16], pa[16], da[32];
+            tmem_ld32_sync(lane_base + kColdA + half * 32, da);   // dA first: its single buffer goes straight back
+            tc_fence_before();
+            mbar_arrive(bar(DW_DAEMPTY));
             const f32x2 r2 = f2_pack(r, r);
+            const uint32_t colS = kColS + sb * 2 * kBI;
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
-                uint32_t m[16], n[16], da[16];
+                uint32_t m[16], n[16];
                 const uint32_t c = half * 32 + sub * 16;
-                tmem_ld16x3_sync(lane_base + kColS + c, lane_base + kColS + kBI + c, lane_base + kColdA + c, m, n, da);
+                tmem_ld16x2_sync(lane_base + colS + c, lane_base + colS + kBI + c, m, n);
+                if (sub == 1) {   // S is in registers: the buffer can take the tile after next
+                    tc_fence_before();
+                    mbar_arrive(bar(DW_SEMPTY + sb));
+                }
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                     const BwdPair x = bwd_pair(f2_pack_bits(m[2 * q], m[2 * q + 1]), f2_pack_bits(n[2 * q], n[2 * q + 1]),
-                                               f2_pack_bits(da[2 * q], da[2 * q + 1]), r2);
+                                               f2_pack_bits(da[sub * 16 + 2 * q], da[sub * 16 + 2 * q + 1]), r2);
                     pm[sub * 8 + q] = f2_to_bf16x2(x.dm);
                     pn[sub * 8 + q] = f2_to_bf16x2(x.dn);
                     pa[sub * 8 + q] = f2_to_bf16x2(f2_mul(x.sn, r2));
                 }
             }
-            tc_fence_before();
-            mbar_arrive(bar(DW_SEMPTY));
             FMHF_TRW(2 + half, i, 2);
             if (!mbar_wait(bar(DW_PEMPTY), (i & 1) ^ 1, ctl, W + 8)) { ok = false; break; }
             FMHF_TRW(2 + half, i, 3);
@@ -663,7 +688,16 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                                         __uint_as_float(o[4 * v + 2]), __uint_as_float(o[4 * v + 3]));
                 }
             }
-            {   // dV (M = 64 accumulator): row r lives in TMEM lane 32*(r/16) + r%16
+            if (kVt) {  // dV^T: lane = column d of dV, tensor-memory column = row of the block; a warp stores 32 consecutive floats per row
+                float *dst = wsb + 2 * plane + row;
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    uint32_t o[16];
+                    tmem_ld16_sync(lane_base + kColV + half * 32 + g * 16, o);
+#pragma unroll
+                    for (int v = 0; v < 16; ++v) dst[(long long)(half * 32 + g * 16 + v) * DH] = __uint_as_float(o[v]);
+                }
+            } else {    // dV (M = 64 accumulator): row r lives in TMEM lane 32*(r/16) + r%16
                 float *dst = wsb + 2 * plane + (long long)(quarter * 16 + (lane & 15)) * DH + c0;
 #pragma unroll
                 for (int g = 0; g < kColsPerHalf / 16; ++g) {

@@ -64,6 +64,10 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x):
+        if x.is_cuda and x.dtype != torch.float32:
+            # one fused kernel each way; differs from the expression below only in where the result is
+            # rounded to bf16 (after the weight instead of before it)
+            return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
         dt = x.dtype
         x = x.float()
         x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps)
@@ -78,9 +82,28 @@ def rotary_tables(S, head_dim, theta, device, dtype):
     return emb.cos().to(dtype), emb.sin().to(dtype)
 
 
-def _rotate_half(x):
-    h = x.shape[-1] // 2
-    return torch.cat((-x[..., h:], x[..., :h]), dim=-1)
+class _Rotary(torch.autograd.Function):
+    """x*cos + rotate_half(x)*sin (modeling_mhffnmoe.py:178-206) written on the two halves of the head
+    dimension, four element-wise kernels each way and nothing saved but the tables:
+    y1 = x1 c1 - x2 s1,  y2 = x2 c2 + x1 s2;   dx1 = g1 c1 + g2 s2,  dx2 = g2 c2 - g1 s1."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        ctx.save_for_backward(cos, sin)
+        h = x.shape[-1] // 2
+        x1, x2, y = x[..., :h], x[..., h:], torch.empty_like(x)
+        torch.mul(x1, cos[..., :h], out=y[..., :h]).addcmul_(x2, sin[..., :h], value=-1)
+        torch.mul(x2, cos[..., h:], out=y[..., h:]).addcmul_(x1, sin[..., h:])
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        cos, sin = ctx.saved_tensors
+        h = g.shape[-1] // 2
+        g1, g2, dx = g[..., :h], g[..., h:], torch.empty_like(g)
+        torch.mul(g1, cos[..., :h], out=dx[..., :h]).addcmul_(g2, sin[..., h:])
+        torch.mul(g2, cos[..., h:], out=dx[..., h:]).addcmul_(g1, sin[..., :h], value=-1)
+        return dx, None, None
 
 
 class Attention(nn.Module):
@@ -98,8 +121,7 @@ class Attention(nn.Module):
         q = self.q_proj(x).view(B, S, self.nh, self.hd).transpose(1, 2)
         k = self.k_proj(x).view(B, S, self.nkv, self.hd).transpose(1, 2)
         v = self.v_proj(x).view(B, S, self.nkv, self.hd).transpose(1, 2)
-        q = q * cos + _rotate_half(q) * sin
-        k = k * cos + _rotate_half(k) * sin
+        q, k = _Rotary.apply(q, cos, sin), _Rotary.apply(k, cos, sin)
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.nkv != self.nh)
         return self.o_proj(o.transpose(1, 2).reshape(B, S, self.nh * self.hd))
 
@@ -198,9 +220,9 @@ class DecoderLM(nn.Module):
         return self.lm_head(self.hidden(ids))
 
     def loss(self, ids):
-        logits = self.forward(ids)
+        logits = self.lm_head(self.hidden(ids)[:, :-1])          # the last position has no label
         V = logits.shape[-1]
-        return F.cross_entropy(logits[:, :-1].float().reshape(-1, V), ids[:, 1:].reshape(-1))
+        return F.cross_entropy(logits.float().reshape(-1, V), ids[:, 1:].reshape(-1))
 
 
 def train_step(model, opt, ids, reducer=None):
