@@ -356,6 +356,8 @@ prologue_bwd_kernel(const ProArgs a, const ProBwdArgs g) {
         }
 }
 
+#include "prologue_mma.cuh"
+
 // out[i] = sum over blocks (in index order) of part[blk][i]
 __global__ void __launch_bounds__(128) prologue_reduce_kernel(const float *part, float *out, long long n, int nblk) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -392,9 +394,13 @@ ProArgs pro_args(const flashmhf_prologue_params &p) {
     return ProArgs{static_cast<const __nv_bfloat16 *>(p.X), p.x_token_stride, p.norm_weight, p.router, p.eps,
                    p.B * p.S, p.H, p.E, p.S, mul, 31 + l};
 }
-// Blocks per head: enough to fill the GPU `per_sm` times over, never more than there are row pairs to deal.
+// E <= 16 runs the MMA kernels (16-token tiles per warp), more sub-networks the per-lane kernels (row pairs).
+bool use_mma(const flashmhf_prologue_params &p) { return p.E <= 16; }
+
+// Blocks per head: enough to fill the GPU `per_sm` times over, never more than there are warp work items to deal.
 int blocks_per_head(const flashmhf_prologue_params &p, int per_sm) {
-    const long long pairs = ((long long)p.B * p.S + kNR - 1) / kNR, most = (pairs + kWarps - 1) / kWarps;
+    const int unit = use_mma(p) ? 16 : kNR;
+    const long long pairs = ((long long)p.B * p.S + unit - 1) / unit, most = (pairs + kWarps - 1) / kWarps;
     const long long want = kNumSMs * per_sm / p.H > 1 ? kNumSMs * per_sm / p.H : 1;
     return (int)(want < most ? want : most);
 }
@@ -422,6 +428,21 @@ cudaError_t launch_bwd(const ProArgs &a, dim3 grid, const ProBwdArgs &g, cudaStr
 }
 
 // dispatch on (d_h, sub-network count rounded up to 16 or 32, RMSNorm on/off)
+#define FMHF_PRO_DISPATCH_MMA(CALL)                                                        \
+    do {                                                                                   \
+        const bool norm = p.norm_weight != nullptr, one = p.E <= 8;                        \
+        if (p.Dh == 128) {                                                                 \
+            if (one) { if (norm) e = CALL(128, 1, true); else e = CALL(128, 1, false); }   \
+            else     { if (norm) e = CALL(128, 2, true); else e = CALL(128, 2, false); }   \
+        } else if (p.Dh == 96) {                                                           \
+            if (one) { if (norm) e = CALL(96, 1, true); else e = CALL(96, 1, false); }     \
+            else     { if (norm) e = CALL(96, 2, true); else e = CALL(96, 2, false); }     \
+        } else {                                                                           \
+            if (one) { if (norm) e = CALL(64, 1, true); else e = CALL(64, 1, false); }     \
+            else     { if (norm) e = CALL(64, 2, true); else e = CALL(64, 2, false); }     \
+        }                                                                                  \
+    } while (0)
+
 #define FMHF_PRO_DISPATCH(CALL)                                                            \
     do {                                                                                   \
         const bool norm = p.norm_weight != nullptr, small = p.E <= 16;                     \
@@ -448,8 +469,11 @@ int prologue_forward(const flashmhf_prologue_params &p, cudaStream_t st, int *n_
     cudaError_t e = cudaSuccess;
     prof_mark(st, kMarkStart);
 #define FMHF_FWD(DH, EP, NORM) launch_fwd<DH, EP, NORM>(a, grid, Q, p.R, st)
-    FMHF_PRO_DISPATCH(FMHF_FWD);
+#define FMHF_FWD_MMA(DH, NT, NORM) launch_fwd_mma<DH, NT, NORM>(a, grid, Q, p.R, st)
+    if (use_mma(p)) FMHF_PRO_DISPATCH_MMA(FMHF_FWD_MMA);
+    else FMHF_PRO_DISPATCH(FMHF_FWD);
 #undef FMHF_FWD
+#undef FMHF_FWD_MMA
     prof_mark(st, kMarkPrologueFwd);
     *n_launch += 1;
     if (e != cudaSuccess) { set_cuda_error(e, "prologue_fwd_kernel launch"); return FLASHMHF_ERR_CUDA; }
@@ -481,8 +505,11 @@ int prologue_backward(const flashmhf_prologue_bwd_params &q, cudaStream_t st, in
     cudaError_t e = cudaSuccess;
     prof_mark(st, kMarkStart);
 #define FMHF_BWD(DH, EP, NORM) launch_bwd<DH, EP, NORM>(a, grid, g, st)
-    FMHF_PRO_DISPATCH(FMHF_BWD);
+#define FMHF_BWD_MMA(DH, NT, NORM) launch_bwd_mma<DH, NT, NORM>(a, grid, g, st)
+    if (use_mma(p)) FMHF_PRO_DISPATCH_MMA(FMHF_BWD_MMA);
+    else FMHF_PRO_DISPATCH(FMHF_BWD);
 #undef FMHF_BWD
+#undef FMHF_BWD_MMA
     prof_mark(st, kMarkPrologueBwd);
     *n_launch += 1;
     if (e != cudaSuccess) { set_cuda_error(e, "prologue_bwd_kernel launch"); return FLASHMHF_ERR_CUDA; }

@@ -1,0 +1,483 @@
+// Prologue kernels for up to 16 sub-networks per head: the three small products of the prologue
+//   logits[t,e]    = sum_d y[t,d] router[d,e]                     (forward, and recomputed in backward)
+//   dy[t,d]       += sum_e dlogits[t,e] router[d,e]
+//   d router[d,e] += sum_t y[t,d] dlogits[t,e]
+// run as warp-level 16x8x16 bf16 `mma.sync` tiles with fp32 accumulation instead of per-lane FMAs and a
+// cross-lane transposing reduction, which cuts the instructions per (token, head) row by about five.
+// These kernels move 0.5-0.8 KB per row and need ~1.4 kFLOP per row for the products: they are bound
+// by HBM, the products take a few percent of the tensor pipe, and the register-fragment form needs no
+// shared-memory or tensor-memory round trip for its 16-row tiles, so the warp-level instruction is
+// the fitting one here (the operator's GEMMs, where throughput matters, use tcgen05).
+//
+// Exactness: y is bf16 already; the fp32 router and the fp32 dlogits are split into bf16 terms
+// (hi + mid + lo, 24 bits) so that products are exact and sums are fp32, as in the fp32 reference math.
+//
+// Work split: a warp owns 16 consecutive tokens of one head at a time; lane (g = lane/4, q = lane%4) holds
+// rows g and g+8 and, of each row, the 16-byte chunks i*4+q (i < d_h/32), i.e. one fully used 64-byte
+// segment per row and load instruction.  The MMA's k index is only a summation index, so k-step ks simply
+// takes the lane's 32-bit registers 2ks and 2ks+1 and the router fragments are permuted to match (col()).
+// Included by prologue.cu inside namespace fmhf::{anonymous}.
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&r)[2], uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(saddr));
+}
+__device__ __forceinline__ float quad_sum(float v) {  // over the 4 lanes that share a row
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    return v;
+}
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
+
+// Memory column of the two bf16 in 32-bit register u of lane quarter q.
+__host__ __device__ constexpr int mma_col(int q, int u) { return ((u >> 2) * 4 + q) * 8 + 2 * (u & 3); }
+
+// v = hi + mid + lo with each term a bf16 (lo absorbs what is left; 24 significant bits in all)
+__device__ __forceinline__ void split3(float v, float &hi, float &mid, float &lo) {
+    hi = bf16_round(v);
+    mid = bf16_round(v - hi);
+    lo = bf16_round(v - hi - mid);
+}
+
+template <int DH, int NT>
+struct MmaLayout {
+    static constexpr int NI = DH / 32, NU = DH / 8, NKS = DH / 16, NKK = (NT + 1) / 2;
+    // shared memory (bytes)
+    static constexpr int kBf = 3 * NKS * NT * 32 * 8;        // logits B fragments: [split][ks][nt][lane] (b0, b1)
+    static constexpr int kB2f = 2 * NKK * NU * 32 * 8;       // router^T B fragments: [split hi/mid][kk][u][lane]
+    static constexpr int kW = DH * 4;
+    static constexpr int kYRow = DH * 2 + 16;                // padded row: ldmatrix rows fall in distinct banks
+    static constexpr int kYTile = 16 * kYRow;
+    static constexpr int kLRow = NT * 16;                    // 8 experts x bf16 per n-tile
+    static constexpr int kLTile = 3 * 16 * kLRow;            // three split terms
+    static constexpr int kOffBf = 0, kOffW = kBf, kOffFwdEnd = kOffW + kW;
+    static constexpr int kOffB2f = kOffFwdEnd, kOffY = kOffB2f + kB2f, kOffL = kOffY + kWarps * kYTile,
+                         kOffBwdEnd = kOffL + kWarps * kLTile;
+};
+
+// Router fragments of head h.  Bf feeds logits = y . router (k = d), B2f feeds dy += dlogits . router^T (k = e).
+template <int DH, int NT, bool BWD>
+__device__ __forceinline__ void build_router_fragments(const float *router_h, int E, uint8_t *smem) {
+    using L = MmaLayout<DH, NT>;
+    uint2 *bf = reinterpret_cast<uint2 *>(smem + L::kOffBf);
+    for (int idx = threadIdx.x; idx < L::NKS * NT * 32; idx += blockDim.x) {
+        const int ln = idx & 31, nt = (idx >> 5) % NT, ks = (idx >> 5) / NT;
+        const int g = ln >> 2, q = ln & 3, e = nt * 8 + g;
+        float v[4], s[3][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {   // (u0,b0) (u0,b1) (u1,b0) (u1,b1)
+            const int d = mma_col(q, 2 * ks + (j >> 1)) + (j & 1);
+            v[j] = e < E ? router_h[d * E + e] : 0.f;
+            split3(v[j], s[0][j], s[1][j], s[2][j]);
+        }
+#pragma unroll
+        for (int t = 0; t < 3; ++t)
+            bf[((t * L::NKS + ks) * NT + nt) * 32 + ln] = make_uint2(pack_bf16(s[t][0], s[t][1]), pack_bf16(s[t][2], s[t][3]));
+    }
+    if (BWD) {
+        uint2 *b2 = reinterpret_cast<uint2 *>(smem + L::kOffB2f);
+        for (int idx = threadIdx.x; idx < L::NKK * L::NU * 32; idx += blockDim.x) {
+            const int ln = idx & 31, u = (idx >> 5) % L::NU, kk = (idx >> 5) / L::NU;
+            const int g = ln >> 2, q = ln & 3;
+            const int d = mma_col(g >> 1, u) + (g & 1);      // the column that accumulator column g of n-tile u stands for
+            float hi[4], mid[4], lo;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {   // experts kk*16 + 2q + {0,1}, then + 8
+                const int e = kk * 16 + (j >> 1) * 8 + 2 * q + (j & 1);
+                const float v = e < E ? router_h[d * E + e] : 0.f;
+                split3(v, hi[j], mid[j], lo);
+            }
+            b2[((0 * L::NKK + kk) * L::NU + u) * 32 + ln] = make_uint2(pack_bf16(hi[0], hi[1]), pack_bf16(hi[2], hi[3]));
+            b2[((1 * L::NKK + kk) * L::NU + u) * 32 + ln] = make_uint2(pack_bf16(mid[0], mid[1]), pack_bf16(mid[2], mid[3]));
+        }
+    }
+}
+
+// Rows g and g+8 of a 16-token tile: load, per-head RMSNorm, logits by MMA, sigmoid and normalisation.
+template <int DH, int NT>
+struct MmaRows {
+    static constexpr int NU = DH / 8;
+    uint32_t x[2][NU];      // bf16 pairs as loaded
+    uint32_t y[2][NU];      // what the router and the operator see
+    float rstd[2], sg[NT][4], D[2];   // sg[nt][j]: row j>>1, sub-network nt*8 + 2q + (j&1)
+};
+
+template <int DH, int NT, bool NORM>
+__device__ __forceinline__ void mma_rows_forward(MmaRows<DH, NT> &r, const ProArgs &a, const uint8_t *smem, int lane) {
+    using L = MmaLayout<DH, NT>;
+    const int q = lane & 3;
+    const float *wsm = reinterpret_cast<const float *>(smem + L::kOffW);
+    if (NORM) {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            float ss = 0.f;
+#pragma unroll
+            for (int u = 0; u < L::NU; ++u) {
+                const float lo = bf16_lo(r.x[k][u]), hi = bf16_hi(r.x[k][u]);
+                ss = fmaf(lo, lo, fmaf(hi, hi, ss));
+            }
+            r.rstd[k] = rsqrtf(quad_sum(ss) * (1.f / (float)DH) + a.eps);
+        }
+#pragma unroll
+        for (int u = 0; u < L::NU; ++u) {
+            const float2 w = *reinterpret_cast<const float2 *>(wsm + mma_col(q, u));
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+                r.y[k][u] = pack_bf16(bf16_lo(r.x[k][u]) * r.rstd[k] * w.x, bf16_hi(r.x[k][u]) * r.rstd[k] * w.y);
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            r.rstd[k] = 1.f;
+#pragma unroll
+            for (int u = 0; u < L::NU; ++u) r.y[k][u] = r.x[k][u];
+        }
+    }
+    float c[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) c[nt][j] = 0.f;
+    const uint2 *bf = reinterpret_cast<const uint2 *>(smem + L::kOffBf);
+#pragma unroll
+    for (int t = 2; t >= 0; --t)            // smallest terms first
+#pragma unroll
+        for (int ks = 0; ks < L::NKS; ++ks)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint2 b = bf[((t * L::NKS + ks) * NT + nt) * 32 + lane];
+                mma16816(c[nt], r.y[0][2 * ks], r.y[1][2 * ks], r.y[0][2 * ks + 1], r.y[1][2 * ks + 1], b.x, b.y);
+            }
+    float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = nt * 8 + 2 * q + (j & 1);
+            const float s = e < a.E ? __fdividef(1.f, 1.f + __expf(-c[nt][j])) : 0.f;
+            r.sg[nt][j] = s;
+            if (j < 2) d0 += s; else d1 += s;
+        }
+    r.D[0] = fmaxf(quad_sum(d0), 1e-20f);
+    r.D[1] = fmaxf(quad_sum(d1), 1e-20f);
+}
+
+template <int DH, int NT>
+__device__ __forceinline__ void mma_load_rows(uint32_t (&dst)[2][DH / 8], const __nv_bfloat16 *p0, const __nv_bfloat16 *p1,
+                                              bool ok0, bool ok1, int q) {
+#pragma unroll
+    for (int i = 0; i < DH / 32; ++i) {
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+        const uint4 v0 = ok0 ? __ldg(reinterpret_cast<const uint4 *>(p0) + i * 4 + q) : z;
+        const uint4 v1 = ok1 ? __ldg(reinterpret_cast<const uint4 *>(p1) + i * 4 + q) : z;
+        dst[0][4 * i] = v0.x; dst[0][4 * i + 1] = v0.y; dst[0][4 * i + 2] = v0.z; dst[0][4 * i + 3] = v0.w;
+        dst[1][4 * i] = v1.x; dst[1][4 * i + 1] = v1.y; dst[1][4 * i + 2] = v1.z; dst[1][4 * i + 3] = v1.w;
+    }
+}
+template <int DH>
+__device__ __forceinline__ void mma_store_row(__nv_bfloat16 *p, const uint32_t (&v)[DH / 8], int q) {
+#pragma unroll
+    for (int i = 0; i < DH / 32; ++i)
+        reinterpret_cast<uint4 *>(p)[i * 4 + q] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+}
+
+// 16-token tile index dealt round-robin over warps, then block columns
+__device__ __forceinline__ long long mma_tile_row(int it, int by, int gy, int warp) {
+    return 16LL * (((long long)it * gy + by) * kWarps + warp);
+}
+
+template <int DH, int NT, bool NORM>
+__global__ void __launch_bounds__(kWarps * 32, 2)
+prologue_fwd_mma_kernel(const ProArgs a, __nv_bfloat16 *Q, float *R) {
+    using L = MmaLayout<DH, NT>;
+    extern __shared__ __align__(16) uint8_t smem_mma[];
+    const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+    build_router_fragments<DH, NT, false>(a.router + (long long)h * DH * a.E, a.E, smem_mma);
+    float *wsm = reinterpret_cast<float *>(smem_mma + L::kOffW);
+    for (int i = threadIdx.x; i < DH; i += blockDim.x) wsm[i] = NORM ? a.W[h * DH + i] : 1.f;
+    __syncthreads();
+    for (int it = 0;; ++it) {
+        const long long t0 = mma_tile_row(it, blockIdx.y, gridDim.y, warp);
+        if (t0 >= a.T) break;
+        const long long tr[2] = {t0 + g, t0 + g + 8};
+        const bool ok[2] = {tr[0] < a.T, tr[1] < a.T};
+        MmaRows<DH, NT> r;
+        mma_load_rows<DH, NT>(r.x, a.X + tr[0] * a.x_tok + h * DH, a.X + tr[1] * a.x_tok + h * DH, ok[0], ok[1], q);
+        mma_rows_forward<DH, NT, NORM>(r, a, smem_mma, lane);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            if (!ok[k]) continue;
+            if (NORM) mma_store_row<DH>(Q + tr[k] * a.x_tok + h * DH, r.y[k], q);
+            const long long b = div_by_s(tr[k], a), s = tr[k] - b * a.S;
+            float *rrow = R + ((b * a.H + h) * a.S + s) * a.E;
+            const float inv = __fdividef(1.f, r.D[k]);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int e = nt * 8 + 2 * q + j;
+                    if (e < a.E) rrow[e] = r.sg[nt][2 * k + j] * inv;
+                }
+        }
+    }
+}
+
+template <int DH, int NT, bool NORM>
+__global__ void __launch_bounds__(kWarps * 32, 1)
+prologue_bwd_mma_kernel(const ProArgs a, const ProBwdArgs gp) {
+    using L = MmaLayout<DH, NT>;
+    constexpr int NU = L::NU, NMT = DH / 16;
+    extern __shared__ __align__(16) uint8_t smem_mma[];
+    const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
+    const int E = a.E, DE = DH * E;
+    build_router_fragments<DH, NT, true>(a.router + (long long)h * DE, E, smem_mma);
+    float *wsm = reinterpret_cast<float *>(smem_mma + L::kOffW);
+    for (int i = threadIdx.x; i < DH; i += blockDim.x) wsm[i] = NORM ? a.W[h * DH + i] : 1.f;
+    __syncthreads();
+    uint8_t *ytile = smem_mma + L::kOffY + warp * L::kYTile;
+    uint8_t *ltile = smem_mma + L::kOffL + warp * L::kLTile;
+    const uint32_t ytile_s = smem_u32(ytile), ltile_s = smem_u32(ltile);
+    const uint2 *b2 = reinterpret_cast<const uint2 *>(smem_mma + L::kOffB2f);
+
+    float racc[NMT][NT][4];   // d router: rows d = mt*16 + g (+8), sub-networks nt*8 + 2q + {0,1}
+    float wacc[NU][2];        // d norm weight of this lane's columns (summed over its rows)
+#pragma unroll
+    for (int mt = 0; mt < NMT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) racc[mt][nt][j] = 0.f;
+#pragma unroll
+    for (int u = 0; u < NU; ++u) wacc[u][0] = wacc[u][1] = 0.f;
+
+    for (int it = 0;; ++it) {
+        const long long t0 = mma_tile_row(it, blockIdx.y, gridDim.y, warp);
+        if (t0 >= a.T) break;
+        const long long tr[2] = {t0 + g, t0 + g + 8};
+        const bool ok[2] = {tr[0] < a.T, tr[1] < a.T};
+        long long roff[2];    // offset of the row's dR
+        const __nv_bfloat16 *dqp[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const long long b = ok[k] ? div_by_s(tr[k], a) : 0, s = ok[k] ? tr[k] - b * a.S : 0;
+            roff[k] = ((b * a.H + h) * a.S + s) * E;
+            dqp[k] = gp.dQ + b * gp.dq_b + (long long)h * gp.dq_h + s * gp.dq_s;
+        }
+        MmaRows<DH, NT> r;
+        uint32_t dq[2][NU];
+        mma_load_rows<DH, NT>(r.x, a.X + tr[0] * a.x_tok + h * DH, a.X + tr[1] * a.x_tok + h * DH, ok[0], ok[1], q);
+        mma_load_rows<DH, NT>(dq, dqp[0], dqp[1], ok[0], ok[1], q);
+        float ge[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int e = nt * 8 + 2 * q + (j & 1);
+                ge[nt][j] = (ok[j >> 1] && e < E) ? __ldg(gp.dR + roff[j >> 1] + e) : 0.f;
+            }
+        mma_rows_forward<DH, NT, NORM>(r, a, smem_mma, lane);
+
+        // y tile at its true columns for the transposed reads of the d router product
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+#pragma unroll
+            for (int i = 0; i < L::NI; ++i)
+                *reinterpret_cast<uint4 *>(ytile + (g + 8 * k) * L::kYRow + (i * 4 + q) * 16) =
+                    make_uint4(r.y[k][4 * i], r.y[k][4 * i + 1], r.y[k][4 * i + 2], r.y[k][4 * i + 3]);
+
+        // R_e = sg_e / D -> dsg_e = (g_e - sum_k g_k R_k) / D ; dlogit_e = dsg_e sg_e (1 - sg_e); a clamped D passes no gradient
+        float inv[2], gr[2] = {0.f, 0.f};
+#pragma unroll
+        for (int k = 0; k < 2; ++k) inv[k] = __fdividef(1.f, r.D[k]);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) gr[j >> 1] = fmaf(ge[nt][j], r.sg[nt][j] * inv[j >> 1], gr[j >> 1]);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) gr[k] = r.D[k] > 1e-20f ? quad_sum(gr[k]) : 0.f;
+        uint32_t dlh[NT][2], dlm[NT][2];   // bf16 pairs of the hi and mid terms: [nt][row]
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                float hi[2], mid[2], lo[2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const float s = r.sg[nt][2 * k + j];
+                    const float dl = (ge[nt][2 * k + j] - gr[k]) * inv[k] * s * (1.f - s);
+                    split3(dl, hi[j], mid[j], lo[j]);
+                }
+                dlh[nt][k] = pack_bf16(hi[0], hi[1]);
+                dlm[nt][k] = pack_bf16(mid[0], mid[1]);
+                const uint32_t dll = pack_bf16(lo[0], lo[1]);
+                // dlogits tile [term][row][sub-network] for the transposed reads
+                const int off = (g + 8 * k) * L::kLRow + nt * 16 + q * 4;
+                *reinterpret_cast<uint32_t *>(ltile + 0 * 16 * L::kLRow + off) = dlh[nt][k];
+                *reinterpret_cast<uint32_t *>(ltile + 1 * 16 * L::kLRow + off) = dlm[nt][k];
+                *reinterpret_cast<uint32_t *>(ltile + 2 * 16 * L::kLRow + off) = dll;
+            }
+        __syncwarp();
+
+        // d router += y^T dlogits : 16 x 8 tiles over d (m) and sub-networks (n), k = the 16 tokens
+        {
+            uint32_t bfr[3][NT][2];
+#pragma unroll
+            for (int t = 0; t < 3; ++t) {
+                const uint32_t base = ltile_s + t * 16 * L::kLRow;
+                if (NT == 2) {      // matrices: (rows 0-7, nt 0) (rows 8-15, nt 0) (rows 0-7, nt 1) (rows 8-15, nt 1)
+                    uint32_t v[4];
+                    ldmatrix_x4_trans(v, base + ((lane & 7) + ((lane >> 3) & 1) * 8) * L::kLRow + (lane >> 4) * 16);
+                    bfr[t][0][0] = v[0]; bfr[t][0][1] = v[1]; bfr[t][NT - 1][0] = v[2]; bfr[t][NT - 1][1] = v[3];
+                } else {
+                    uint32_t v[2];
+                    ldmatrix_x2_trans(v, base + ((lane & 7) + ((lane >> 3) & 1) * 8) * L::kLRow);
+                    bfr[t][0][0] = v[0]; bfr[t][0][1] = v[1];
+                }
+            }
+#pragma unroll
+            for (int mt = 0; mt < NMT; ++mt) {
+                uint32_t av[4];     // matrices: (rows 0-7, cols c0) (rows 0-7, c0+8) (rows 8-15, c0) (rows 8-15, c0+8)
+                ldmatrix_x4_trans(av, ytile_s + ((lane & 7) + (lane >> 4) * 8) * L::kYRow + (mt * 16 + ((lane >> 3) & 1) * 8) * 2);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int t = 2; t >= 0; --t) mma16816(racc[mt][nt], av[0], av[1], av[2], av[3], bfr[t][nt][0], bfr[t][nt][1]);
+            }
+        }
+        __syncwarp();   // the tiles are rewritten in the next iteration
+
+        // dy = dQ + dlogits . router^T : accumulator n-tile u holds this lane's own columns mma_col(q,u)+{0,1}
+        float dy[NU][4];
+#pragma unroll
+        for (int u = 0; u < NU; ++u) {
+            dy[u][0] = bf16_lo(dq[0][u]); dy[u][1] = bf16_hi(dq[0][u]);
+            dy[u][2] = bf16_lo(dq[1][u]); dy[u][3] = bf16_hi(dq[1][u]);
+        }
+#pragma unroll
+        for (int kk = 0; kk < L::NKK; ++kk) {
+            const bool two = 2 * kk + 1 < NT;
+            const uint32_t ah0 = dlh[2 * kk][0], ah1 = dlh[2 * kk][1], ah2 = two ? dlh[two ? 2 * kk + 1 : 0][0] : 0u,
+                           ah3 = two ? dlh[two ? 2 * kk + 1 : 0][1] : 0u;
+            const uint32_t am0 = dlm[2 * kk][0], am1 = dlm[2 * kk][1], am2 = two ? dlm[two ? 2 * kk + 1 : 0][0] : 0u,
+                           am3 = two ? dlm[two ? 2 * kk + 1 : 0][1] : 0u;
+#pragma unroll
+            for (int u = 0; u < NU; ++u) {
+                const uint2 bh = b2[((0 * L::NKK + kk) * NU + u) * 32 + lane], bm = b2[((1 * L::NKK + kk) * NU + u) * 32 + lane];
+                mma16816(dy[u], am0, am1, am2, am3, bh.x, bh.y);
+                mma16816(dy[u], ah0, ah1, ah2, ah3, bm.x, bm.y);
+                mma16816(dy[u], ah0, ah1, ah2, ah3, bh.x, bh.y);
+            }
+        }
+
+        // RMSNorm backward: y_d = w_d x_d rstd ; dx_d = rstd w_d dy_d - rstd^3 x_d mean_k(w_k dy_k x_k) ; dw_d += dy_d x_d rstd
+        uint32_t dx[2][NU];
+        if (NORM) {
+            float c[2] = {0.f, 0.f};
+#pragma unroll
+            for (int u = 0; u < NU; ++u) {
+                const float2 w = *reinterpret_cast<const float2 *>(wsm + mma_col(q, u));
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    const float x0 = bf16_lo(r.x[k][u]), x1 = bf16_hi(r.x[k][u]);
+                    const float p0 = dy[u][2 * k] * x0, p1 = dy[u][2 * k + 1] * x1;
+                    c[k] = fmaf(w.x, p0, fmaf(w.y, p1, c[k]));
+                    wacc[u][0] = fmaf(p0, r.rstd[k], wacc[u][0]);
+                    wacc[u][1] = fmaf(p1, r.rstd[k], wacc[u][1]);
+                }
+            }
+            float r3c[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) r3c[k] = r.rstd[k] * r.rstd[k] * r.rstd[k] * quad_sum(c[k]) * (1.f / (float)DH);
+#pragma unroll
+            for (int u = 0; u < NU; ++u) {
+                const float2 w = *reinterpret_cast<const float2 *>(wsm + mma_col(q, u));
+#pragma unroll
+                for (int k = 0; k < 2; ++k)
+                    dx[k][u] = pack_bf16(r.rstd[k] * w.x * dy[u][2 * k] - r3c[k] * bf16_lo(r.x[k][u]),
+                                         r.rstd[k] * w.y * dy[u][2 * k + 1] - r3c[k] * bf16_hi(r.x[k][u]));
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < NU; ++u)
+#pragma unroll
+                for (int k = 0; k < 2; ++k) dx[k][u] = pack_bf16(dy[u][2 * k], dy[u][2 * k + 1]);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+            if (ok[k]) mma_store_row<DH>(gp.dX + tr[k] * a.x_tok + h * DH, dx[k], q);
+    }
+
+    // warps' accumulators -> shared -> this block's partial sums (fixed order).  The tiles and fragments are
+    // no longer needed: the per-warp sums reuse shared memory from the start.
+    __syncthreads();
+    float *acc_r = reinterpret_cast<float *>(smem_mma), *acc_w = acc_r + kWarps * DE;
+    float *my_r = acc_r + warp * DE, *my_w = acc_w + warp * DH;
+#pragma unroll
+    for (int mt = 0; mt < NMT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int d = mt * 16 + g + 8 * (j >> 1), e = nt * 8 + 2 * q + (j & 1);
+                if (e < E) my_r[d * E + e] = racc[mt][nt][j];
+            }
+#pragma unroll
+    for (int u = 0; u < NU; ++u)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            float v = wacc[u][j];   // sum over the 8 lanes that hold the same columns
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            if (g == 0) my_w[mma_col(q, u) + j] = v;
+        }
+    __syncthreads();
+    for (int i = threadIdx.x; i < DE; i += blockDim.x) {
+        float v = 0.f;
+#pragma unroll
+        for (int wp = 0; wp < kWarps; ++wp) v += acc_r[wp * DE + i];
+        gp.part_router[((long long)blockIdx.y * a.H + h) * DE + i] = v;
+    }
+    if (NORM)
+        for (int i = threadIdx.x; i < DH; i += blockDim.x) {
+            float v = 0.f;
+#pragma unroll
+            for (int wp = 0; wp < kWarps; ++wp) v += acc_w[wp * DH + i];
+            gp.part_w[((long long)blockIdx.y * a.H + h) * DH + i] = v;
+        }
+}
+
+template <int DH, int NT>
+size_t mma_fwd_smem() { return (size_t)MmaLayout<DH, NT>::kOffFwdEnd; }
+template <int DH, int NT>
+size_t mma_bwd_smem(int E) {
+    const size_t loop = (size_t)MmaLayout<DH, NT>::kOffBwdEnd, fin = (size_t)kWarps * ((size_t)DH * E + DH) * sizeof(float);
+    return loop > fin ? loop : fin;
+}
+
+template <int DH, int NT, bool NORM>
+cudaError_t launch_fwd_mma(const ProArgs &a, dim3 grid, __nv_bfloat16 *Q, float *R, cudaStream_t st) {
+    const size_t smem = mma_fwd_smem<DH, NT>();
+    cudaError_t e = cudaFuncSetAttribute(prologue_fwd_mma_kernel<DH, NT, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    prologue_fwd_mma_kernel<DH, NT, NORM><<<grid, kWarps * 32, smem, st>>>(a, Q, R);
+    return cudaGetLastError();
+}
+template <int DH, int NT, bool NORM>
+cudaError_t launch_bwd_mma(const ProArgs &a, dim3 grid, const ProBwdArgs &g, cudaStream_t st) {
+    const size_t smem = mma_bwd_smem<DH, NT>(a.E);
+    cudaError_t e = cudaFuncSetAttribute(prologue_bwd_mma_kernel<DH, NT, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    prologue_bwd_mma_kernel<DH, NT, NORM><<<grid, kWarps * 32, smem, st>>>(a, g);
+    return cudaGetLastError();
+}
