@@ -185,3 +185,34 @@ def test_large_shape_linearity_property():
     assert orc.rel_l2((O1 + O2).cpu(), O12.cpu()) < TOL_BF16
     sub = fm.forward_raw(Q[1:3, :, 256:1280].contiguous(), K, U, V, R1[1:3, :, 256:1280].contiguous())
     assert torch.equal(sub, fm.forward_raw(Q, K, U, V, R1)[1:3, :, 256:1280])
+
+
+def test_forward_and_backward_replay_from_a_cuda_graph():
+    """The calls only enqueue kernels on the given stream, so a stream capture records them; replaying the graph on
+    new input values (same buffers) must give what the eager calls give.  Covers the split (short) and the plain path."""
+    import flashmhf_b200 as fm
+    from flashmhf_b200 import _lib
+    for shape in ((2, 2, 300, 128, 3, 128), (64, 4, 1, 128, 2, 128)):
+        B, H, S, dh, E, de = shape
+        Q, K, U, V, R, dO = (t.cuda() for t in orc.make_op_inputs(B, H, S, dh, E, de, seed=77, dtype=torch.bfloat16))
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                fm.forward_raw(Q, K, U, V, R)
+                fm.backward_raw(Q, K, U, V, R, dO)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            O = fm.forward_raw(Q, K, U, V, R)
+            grads = fm.backward_raw(Q, K, U, V, R, dO)
+        Q2, _, _, _, R2, dO2 = (t.cuda() for t in orc.make_op_inputs(B, H, S, dh, E, de, seed=78, dtype=torch.bfloat16))
+        Q.copy_(Q2); R.copy_(R2); dO.copy_(dO2)
+        graph.replay()
+        torch.cuda.synchronize()
+        got = [O.clone()] + [g.clone() for g in grads]
+        want = [fm.forward_raw(Q, K, U, V, R)] + list(fm.backward_raw(Q, K, U, V, R, dO))
+        torch.cuda.synchronize()
+        for a, b in zip(got, want):
+            assert torch.equal(a, b)
+        _lib.device_status()
