@@ -1,0 +1,141 @@
+"""Operator and LM measurements beyond the one line bench.py prints.
+
+    python -m flashmhf_b200.opbench --sweep      # operator forward+backward over a grid of shapes, next to a dense SwiGLU
+    python -m flashmhf_b200.opbench --lm         # forward tokens/s of the 128M and 1.3B LMs, training step of the 370M LM
+
+Everything is timed with CUDA events after warm-up; inputs are seeded synthetic tensors (Q ~ N(0,1),
+weights ~ N(0, 0.02), routing weights = normalised sigmoid of N(0,1) logits, dO ~ N(0,1)).
+Algorithmic FLOPs of the operator: 18*T*H*I*d_h for forward+backward (recompute not counted); the dense
+SwiGLU with the same parameter count (W_g, W_u, W_d of shape [I, H*d_h]) has the same count.
+Prints markdown tables.
+"""
+import argparse
+import json
+import os
+
+import torch
+
+NOMINAL_TFLOPS = 2250.0
+
+
+def _measured_sustained():
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    try:
+        with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops_sustained"])
+    except (OSError, KeyError, ValueError):
+        return 1400.0
+
+
+def _time(fn, budget_s=0.25, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(); fn(); e1.record(); torch.cuda.synchronize()
+    n = max(3, min(200, int(budget_s * 1e3 / max(e0.elapsed_time(e1), 1e-3))))
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record(); torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / n
+
+
+def sweep(args):
+    import flashmhf_b200 as fm
+    from flashmhf_b200 import _lib
+    sustained = _measured_sustained()
+    dev = torch.device("cuda")
+    print("| T | d_h | H | E | d_e | fwd ms | bwd ms | TFLOP/s | of nominal 2250 | of measured %.0f | peak MB | dense SwiGLU TFLOP/s | ratio |" % sustained)
+    print("|---|---|---|---|---|---|---|---|---|---|---|---|---|")
+    shapes = []
+    for dh, des in ((128, (320, 256)), (64, (192,))):
+        for de in des:
+            for H in (8, 16):
+                for E in (8, 16, 32):
+                    for T in (4096, 16384, 65536, 262144):
+                        shapes.append((T, dh, H, E, de))
+    if args.quick:
+        shapes = [s for s in shapes if s[0] in (4096, 65536) and s[3] != 16]
+    for T, dh, H, E, de in shapes:
+        B, S = T // 4096, 4096
+        g = torch.Generator(device=dev).manual_seed(0)
+        Q = torch.randn(B, H, S, dh, device=dev, generator=g).bfloat16()
+        dO = torch.randn(B, H, S, dh, device=dev, generator=g).bfloat16()
+        K, U, V = (torch.randn(H, E, de, dh, device=dev, generator=g).mul(0.02).bfloat16() for _ in range(3))
+        R = torch.randn(B, H, S, E, device=dev, generator=g).sigmoid()
+        R = R / R.sum(-1, keepdim=True)
+        torch.cuda.reset_peak_memory_stats()
+        base = torch.cuda.memory_allocated()
+        tf = _time(lambda: fm.forward_raw(Q, K, U, V, R))
+        tb = _time(lambda: fm.backward_raw(Q, K, U, V, R, dO))
+        peak = (torch.cuda.max_memory_allocated() - base) / 2**20
+        _lib.device_status()
+        flops = 18.0 * T * H * E * de * dh
+        tfl = flops / ((tf + tb) * 1e-3) / 1e12
+        # dense SwiGLU of the same parameter count, torch matmul + autograd
+        hid, I = H * dh, E * de
+        X = Q.transpose(1, 2).reshape(T, hid).contiguous().requires_grad_(True)
+        Wg, Wu, Wd = (torch.randn(I, hid, device=dev, generator=g).mul(0.02).bfloat16().requires_grad_(True) for _ in range(3))
+        gO = dO.transpose(1, 2).reshape(T, hid).contiguous()
+
+        def dense():
+            y = (torch.nn.functional.silu(X @ Wg.t()) * (X @ Wu.t())) @ Wd
+            y.backward(gO)
+            X.grad = Wg.grad = Wu.grad = Wd.grad = None
+        td = _time(dense)
+        tfd = flops / (td * 1e-3) / 1e12
+        print(f"| {T} | {dh} | {H} | {E} | {de} | {tf:.3f} | {tb:.3f} | {tfl:.0f} | {tfl / NOMINAL_TFLOPS:.3f} | {tfl / sustained:.3f} | "
+              f"{peak:.0f} | {tfd:.0f} | {tfl / tfd:.2f} |", flush=True)
+        del Q, dO, K, U, V, R, X, Wg, Wu, Wd, gO
+        torch.cuda.empty_cache()
+
+
+def lm_runs(args):
+    from flashmhf_b200 import _lib, lm
+    dev = torch.device("cuda")
+    print("| model | parameters | batch x seq | pass | ms | tokens/s | model TFLOP/s | FFN kernels' share |")
+    print("|---|---|---|---|---|---|---|---|")
+    for name, cfg, B, S in (("128M", lm.LMConfig.lm_128m(), 8, 2048), ("1.3B", lm.LMConfig.lm_1p3b(), 4, 8192)):
+        model = lm.DecoderLM(cfg).init_weights(seed=0).to(dev).to(torch.bfloat16)
+        ids = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(0)).to(dev)
+        with torch.no_grad():
+            ms = _time(lambda: model(ids), budget_s=1.0)
+            _lib.profile_begin(4096)
+            model(ids)
+            ours = sum(sum(v) for v in _lib.profile_end().values())
+        fl = lm.train_flops_per_token(cfg, S) / 3 * B * S
+        print(f"| {name} | {lm.param_count(model) / 1e6:.0f} M | {B} x {S} | forward | {ms:.2f} | {B * S / (ms * 1e-3):.0f} | "
+              f"{fl / (ms * 1e-3) / 1e12:.0f} | {ours / ms:.2f} |", flush=True)
+        del model
+        torch.cuda.empty_cache()
+    cfg, B, S = lm.LMConfig.lm_370m(), 16, 2048
+    model = lm.DecoderLM(cfg).init_weights(seed=0).to(dev).to(torch.bfloat16)
+    opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+    ids = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(0)).to(dev)
+    ms = _time(lambda: lm.train_step(model, opt, ids), budget_s=2.0)
+    _lib.profile_begin(4096)
+    lm.train_step(model, opt, ids)
+    ours = sum(sum(v) for v in _lib.profile_end().values())
+    fl = lm.train_flops_per_token(cfg, S) * B * S
+    print(f"| 370M | {lm.param_count(model) / 1e6:.0f} M | {B} x {S} | forward + backward + AdamW | {ms:.2f} | {B * S / (ms * 1e-3):.0f} | "
+          f"{fl / (ms * 1e-3) / 1e12:.0f} | {ours / ms:.2f} |", flush=True)
+    print(f"\npeak memory of the 370M training step: {torch.cuda.max_memory_allocated() / 2**30:.1f} GiB")
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--sweep", action="store_true")
+    ap.add_argument("--lm", action="store_true")
+    ap.add_argument("--quick", action="store_true", help="a quarter of the sweep grid")
+    args = ap.parse_args()
+    if not (args.sweep or args.lm):
+        ap.error("choose --sweep and/or --lm")
+    if args.sweep:
+        sweep(args)
+    if args.lm:
+        lm_runs(args)
+
+
+if __name__ == "__main__":
+    main()
