@@ -143,8 +143,8 @@ def run_reference(args, rank, world):
     t0 = time.perf_counter()
     probe()
     per_token = (time.perf_counter() - t0) / 1024
-    budget_s = 120.0
-    sample_S = int(budget_s / max(1, args.steps + args.warmup) / per_token)
+    target_s = 120.0
+    sample_S = int(target_s / max(1, args.steps + args.warmup) / per_token)
     sample_S = max(256, min(CPU_SAMPLE_TOKENS, sample_S // 128 * 128))
     step = make(sample_S)
     for _ in range(args.warmup):

@@ -27,13 +27,13 @@ def _measured_sustained():
         return 1400.0
 
 
-def _time(fn, budget_s=0.25, warmup=3):
+def _time(fn, target_s=0.25, warmup=3):
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(); fn(); e1.record(); torch.cuda.synchronize()
-    n = max(3, min(200, int(budget_s * 1e3 / max(e0.elapsed_time(e1), 1e-3))))
+    n = max(3, min(200, int(target_s * 1e3 / max(e0.elapsed_time(e1), 1e-3))))
     e0.record()
     for _ in range(n):
         fn()
@@ -100,7 +100,7 @@ def lm_runs(args):
         model = lm.DecoderLM(cfg).init_weights(seed=0).to(dev).to(torch.bfloat16)
         ids = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(0)).to(dev)
         with torch.no_grad():
-            ms = _time(lambda: model(ids), budget_s=1.0)
+            ms = _time(lambda: model(ids), target_s=1.0)
             _lib.profile_begin(4096)
             model(ids)
             ours = sum(sum(v) for v in _lib.profile_end().values())
@@ -113,7 +113,7 @@ def lm_runs(args):
     model = lm.DecoderLM(cfg).init_weights(seed=0).to(dev).to(torch.bfloat16)
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
     ids = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(0)).to(dev)
-    ms = _time(lambda: lm.train_step(model, opt, ids), budget_s=2.0)
+    ms = _time(lambda: lm.train_step(model, opt, ids), target_s=2.0)
     _lib.profile_begin(4096)
     lm.train_step(model, opt, ids)
     ours = sum(sum(v) for v in _lib.profile_end().values())

@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this folder from the UNMODIFIED reference layer.
 
-Run where the reference checkout is available (default /root/reference, or pass its path):
+Run where a checkout of the reference is available:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It imports ``models/flashmhf/modeling_mhffnmoe.py`` without touching it (a stub package
 ``transformers.models.mhffnmoe`` satisfies its relative imports; ``transformers.utils.LossKwargs``
@@ -119,7 +119,9 @@ def run_case(C, M, name, *, hidden, inter, H, Hkuv, E, B, S, rmsnorm, seed, full
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python %s /path/to/reference" % os.path.basename(__file__))
+    ref_root = sys.argv[1]
     torch.manual_seed(0)
     C, M = load_reference(ref_root)
     # tiny layer, every tensor stored

@@ -1,6 +1,6 @@
 """Generate ``lm_tiny.npz``: a two-layer decoder LM composed from the UNMODIFIED reference modules.
 
-    python tests/golden/make_golden_lm.py [/path/to/reference]
+    python tests/golden/make_golden_lm.py /path/to/reference
 
 The reference's ``MHFFNMoEForCausalLM`` does not construct under the transformers release in this
 image, so the model is assembled from the reference's own building blocks -- ``nn.Embedding``,
@@ -28,7 +28,9 @@ B, S, SEED = 2, 24, 11
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python %s /path/to/reference" % os.path.basename(__file__))
+    ref_root = sys.argv[1]
     C, M = load_reference(ref_root)
     cfg = C.MHFFNMoEConfig(mhffnmoe_use_flash=False, mhffnmoe_custom_init=True, max_position_embeddings=64, **CFG)
     cfg._attn_implementation = "eager"

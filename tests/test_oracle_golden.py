@@ -74,7 +74,7 @@ def test_explicit_backward_equals_autograd(dt):
         assert orc.rel_l2(a, b) < 1e-13
 
 
-def test_bf16_eager_vs_fp32_oracle_budget():
+def test_bf16_eager_vs_fp32_oracle_headroom():
     """The eager path in bf16 sits well inside the 1e-2 tolerance of the fp32 evaluation of the same inputs."""
     Q, K, U, V, R = orc.make_op_inputs(1, 2, 64, 64, 2, 64, seed=7, dtype=torch.bfloat16, with_dO=False)
     o16 = orc.mhffn_forward(Q, K, U, V, R)
