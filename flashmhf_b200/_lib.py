@@ -16,7 +16,8 @@ EXPORTS = ("flashmhf_abi_version", "flashmhf_forward_workspace_bytes", "flashmhf
            "flashmhf_backward_workspace_bytes", "flashmhf_backward", "flashmhf_device_status",
            "flashmhf_launch_count", "flashmhf_profile_begin", "flashmhf_profile_end",
            "flashmhf_backward_static_scratch", "flashmhf_prologue_forward",
-           "flashmhf_prologue_backward_workspace_bytes", "flashmhf_prologue_backward")
+           "flashmhf_prologue_backward_workspace_bytes", "flashmhf_prologue_backward", "flashmhf_lm_rope",
+           "flashmhf_lm_rmsnorm_forward", "flashmhf_lm_rmsnorm_backward_workspace_bytes", "flashmhf_lm_rmsnorm_backward")
 
 
 class Tensor(C.Structure):
@@ -93,6 +94,16 @@ def load():
         lib.flashmhf_prologue_backward_workspace_bytes.argtypes = [C.POINTER(PrologueParams)]
         lib.flashmhf_prologue_backward.restype = C.c_int
         lib.flashmhf_prologue_backward.argtypes = [C.POINTER(PrologueBwdParams), C.c_void_p]
+        lib.flashmhf_lm_rope.restype = C.c_int
+        lib.flashmhf_lm_rope.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
+                                         C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p]
+        lib.flashmhf_lm_rmsnorm_forward.restype = C.c_int
+        lib.flashmhf_lm_rmsnorm_forward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_float, C.c_void_p]
+        lib.flashmhf_lm_rmsnorm_backward_workspace_bytes.restype = C.c_size_t
+        lib.flashmhf_lm_rmsnorm_backward_workspace_bytes.argtypes = [C.c_int64, C.c_int32]
+        lib.flashmhf_lm_rmsnorm_backward.restype = C.c_int
+        lib.flashmhf_lm_rmsnorm_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                     C.c_size_t, C.c_int64, C.c_int32, C.c_float, C.c_void_p]
         lib.flashmhf_device_status.restype = C.c_int
         lib.flashmhf_device_status.argtypes = [C.POINTER(C.c_int)]
         lib.flashmhf_launch_count.restype = C.c_uint64

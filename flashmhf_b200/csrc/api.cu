@@ -223,6 +223,41 @@ int flashmhf_prologue_backward(const flashmhf_prologue_bwd_params *p, void *stre
     return rc;
 }
 
+int flashmhf_lm_rope(const void *x, void *y, const float *cos_t, const float *sin_t, int64_t tokens, int32_t S,
+                     int32_t heads, int32_t head_dim, int64_t x_token_stride, int64_t y_token_stride, int32_t transpose,
+                     void *stream) {
+    int rc = check_arch();
+    if (rc) return rc;
+    int n = 0;
+    rc = lm_rope(x, y, cos_t, sin_t, tokens, S, heads, head_dim, x_token_stride, y_token_stride, transpose,
+                 static_cast<cudaStream_t>(stream), &n);
+    g_launches += (uint64_t)n;
+    return rc;
+}
+
+int flashmhf_lm_rmsnorm_forward(const void *x, const float *w, void *y, int64_t rows, int32_t n, float eps, void *stream) {
+    int rc = check_arch();
+    if (rc) return rc;
+    int nl = 0;
+    rc = lm_rmsnorm_forward(x, w, y, rows, n, eps, static_cast<cudaStream_t>(stream), &nl);
+    g_launches += (uint64_t)nl;
+    return rc;
+}
+
+size_t flashmhf_lm_rmsnorm_backward_workspace_bytes(int64_t rows, int32_t n) {
+    return lm_rmsnorm_backward_workspace_bytes(rows, n);
+}
+
+int flashmhf_lm_rmsnorm_backward(const void *x, const float *w, const void *g, void *dx, float *dw, void *workspace,
+                                 size_t workspace_bytes, int64_t rows, int32_t n, float eps, void *stream) {
+    int rc = check_arch();
+    if (rc) return rc;
+    int nl = 0;
+    rc = lm_rmsnorm_backward(x, w, g, dx, dw, workspace, workspace_bytes, rows, n, eps, static_cast<cudaStream_t>(stream), &nl);
+    g_launches += (uint64_t)nl;
+    return rc;
+}
+
 int flashmhf_profile_begin(int max_marks) {
     std::lock_guard<std::mutex> lk(g_mu);
     if (g_prof.on || max_marks < 2) return FLASHMHF_ERR_BAD_SHAPE;

@@ -27,6 +27,14 @@ int prologue_forward(const flashmhf_prologue_params &p, cudaStream_t st, int *n_
 size_t prologue_backward_workspace_bytes(const flashmhf_prologue_params &p);
 int prologue_backward(const flashmhf_prologue_bwd_params &p, cudaStream_t st, int *n_launch);
 
+// ---- helpers for the measurement LM: rotary embedding and hidden-size RMSNorm (lm_aux.cu) ----
+int lm_rope(const void *x, void *y, const float *cos_t, const float *sin_t, long long tokens, int S, int heads, int hd,
+            long long x_tok, long long y_tok, int transpose, cudaStream_t st, int *n_launch);
+int lm_rmsnorm_forward(const void *x, const float *w, void *y, long long rows, int n, float eps, cudaStream_t st, int *n_launch);
+size_t lm_rmsnorm_backward_workspace_bytes(long long rows, int n);
+int lm_rmsnorm_backward(const void *x, const float *w, const void *g, void *dx, float *dw, void *workspace,
+                        size_t workspace_bytes, long long rows, int n, float eps, cudaStream_t st, int *n_launch);
+
 void set_cuda_error(cudaError_t e, const char *where);
 
 // Kernel-boundary marks for the profiling aid (flashmhf_profile_begin/end): records an event on

@@ -3,9 +3,10 @@
 The architecture and every parameter name follow the reference model
 (models/flashmhf/modeling_mhffnmoe.py: decoder layer :601-652, attention :523-598, RMSNorm :73-90,
 rotary tables :164-175, FFN layer :256-431, model :784-921, LM head :1055-1090), so a reference
-state dict loads with ``load_state_dict``.  Only the FFN layer is this package's own code (the fused
-prologue + the CUDA operator); attention, norms, embeddings and the loss are plain PyTorch calls: they are
-the surroundings the operator is measured in, not part of it.
+state dict loads with ``load_state_dict``.  The FFN layer is this package's code (the fused prologue + the
+CUDA operator), and on CUDA bf16 tensors the rotary embedding and the hidden-size RMSNorm run through two small
+kernels of the same library (lm_ops.py); attention, projections, embeddings and the loss are plain PyTorch
+calls: they are the surroundings the operator is measured in, not part of it.
 
 ``ffn`` lets a caller substitute the FFN layer function; the default is the CUDA layer and there is
 no CPU stand-in for it in this package.
@@ -64,9 +65,12 @@ class RMSNorm(nn.Module):
         self.eps = eps
 
     def forward(self, x):
-        if x.is_cuda and x.dtype != torch.float32:
-            # one fused kernel each way; differs from the expression below only in where the result is
-            # rounded to bf16 (after the weight instead of before it)
+        if x.is_cuda and x.dtype == torch.bfloat16:
+            # one kernel each way; differs from the expression below only in where the result is rounded to
+            # bf16 (after the weight instead of before it)
+            from . import lm_ops
+            if x.shape[-1] in lm_ops.NORM_SIZES:
+                return lm_ops.RMSNormFunction.apply(x, self.weight, self.eps)
             return F.rms_norm(x, (x.shape[-1],), self.weight, self.eps)
         dt = x.dtype
         x = x.float()
@@ -118,10 +122,16 @@ class Attention(nn.Module):
 
     def forward(self, x, cos, sin):
         B, S, _ = x.shape
-        q = self.q_proj(x).view(B, S, self.nh, self.hd).transpose(1, 2)
-        k = self.k_proj(x).view(B, S, self.nkv, self.hd).transpose(1, 2)
+        q = self.q_proj(x).view(B, S, self.nh, self.hd)
+        k = self.k_proj(x).view(B, S, self.nkv, self.hd)
         v = self.v_proj(x).view(B, S, self.nkv, self.hd).transpose(1, 2)
-        q, k = _Rotary.apply(q, cos, sin), _Rotary.apply(k, cos, sin)
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.hd % 16 == 0:
+            from . import lm_ops
+            ct, st = lm_ops.rotary_tables_f32(cos, sin)
+            q = lm_ops.RotaryFunction.apply(q, ct, st).transpose(1, 2)
+            k = lm_ops.RotaryFunction.apply(k, ct, st).transpose(1, 2)
+        else:
+            q, k = _Rotary.apply(q.transpose(1, 2), cos, sin), _Rotary.apply(k.transpose(1, 2), cos, sin)
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.nkv != self.nh)
         return self.o_proj(o.transpose(1, 2).reshape(B, S, self.nh * self.hd))
 

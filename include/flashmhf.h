@@ -171,6 +171,24 @@ int flashmhf_prologue_forward(const flashmhf_prologue_params *p, void *stream);
 size_t flashmhf_prologue_backward_workspace_bytes(const flashmhf_prologue_params *p);
 int flashmhf_prologue_backward(const flashmhf_prologue_bwd_params *p, void *stream);
 
+/* ---- Helpers for the measurement LM (flashmhf_b200/lm.py), outside the operator -------------------
+ * Rotary position embedding on [tokens, heads, head_dim] bf16 (token strides in elements, multiples of 8):
+ *   y[..., :h] = x[..., :h] cos - x[..., h:] sin ;  y[..., h:] = x[..., h:] cos + x[..., :h] sin,  h = head_dim/2,
+ * with cos_t, sin_t fp32 [S, h] and the position of token t being t % S; transpose != 0 applies the transposed
+ * rotation (the backward).  Replaces modeling_mhffnmoe.py:178-206 (apply_rotary_pos_emb).  x == y is allowed. */
+int flashmhf_lm_rope(const void *x, void *y, const float *cos_t, const float *sin_t, int64_t tokens, int32_t S,
+                     int32_t heads, int32_t head_dim, int64_t x_token_stride, int64_t y_token_stride, int32_t transpose,
+                     void *stream);
+
+/* RMSNorm over contiguous rows of n in {768, 1024, 2048} bf16 elements with an fp32 weight [n]:
+ * y = x * rsqrt(mean(x^2) + eps) * w (fp32 arithmetic, one rounding).  Replaces modeling_mhffnmoe.py:82-87.
+ * Backward: dx (bf16) and dw (fp32 [n]) from x, w and the gradient g; workspace of
+ * flashmhf_lm_rmsnorm_backward_workspace_bytes(rows, n) bytes, 16-byte aligned; deterministic. */
+int flashmhf_lm_rmsnorm_forward(const void *x, const float *w, void *y, int64_t rows, int32_t n, float eps, void *stream);
+size_t flashmhf_lm_rmsnorm_backward_workspace_bytes(int64_t rows, int32_t n);
+int flashmhf_lm_rmsnorm_backward(const void *x, const float *w, const void *g, void *dx, float *dw, void *workspace,
+                                 size_t workspace_bytes, int64_t rows, int32_t n, float eps, void *stream);
+
 /* SYNCHRONOUS.  Waits for the current device, then reads and clears the status word the kernels
  * write when a bounded wait runs out.  *code = 0 if none did; otherwise a kernel/role identifier,
  * and the call returns FLASHMHF_ERR_DEVICE_TIMEOUT.  Reference counterpart: none. */
