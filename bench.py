@@ -32,7 +32,7 @@ NOMINAL_BF16_TFLOPS = 2250.0
 # DRAM bytes (read + write) per launch on this workload, from one `ncu --set full` capture of each kernel
 # (profiles/ncu_full_fwd_bwd_kernels_370m_layer_op.md).  Reported as roofline.traffic; the kernels are
 # tensor-bound, so this only shows that nothing is re-read from HBM (Q, dO, O, dQ once; weights from L2).
-NCU_DRAM_BYTES_PER_LAUNCH = {"fwd_kernel": 135.2e6, "bwd_dq_kernel": 227.9e6, "bwd_dw_kernel": 231.7e6}
+NCU_DRAM_BYTES_PER_LAUNCH = {"fwd_kernel": 136.1e6, "bwd_dq_kernel": 227.3e6, "bwd_dw_kernel": 226.5e6}
 CPU_SAMPLE_TOKENS = 8192   # one batch row of this many tokens per CPU pass (~0.5 s on 16 cores)
 
 
