@@ -206,7 +206,7 @@ def lm_train_370m(args, rank, world, dev, sync_all):
             "batch_per_gpu": Bt, "seq_len": St, "n_params": lm.param_count(model), "optimizer": "AdamW (torch fused), bf16 parameters",
             "model_tflops_per_gpu": flops / (ms * 1e-3) / 1e12,
             "ffn_kernels_ms_per_step": ours_ms, "ffn_kernels_share": ours_ms / ms,
-            "ffn_kernel_launches_per_step": (_lib.launch_count() - launches0) / args.lm_steps,
+            "library_kernel_launches_per_step": (_lib.launch_count() - launches0) / args.lm_steps,
             "loss_first_last": [first_loss, float(loss_host)],
             "outside_the_ffn": "attention = torch scaled_dot_product_attention, projections = cuBLAS, loss = torch cross_entropy",
             "parallelism": f"dp{world}" + (" + per-layer NCCL all-reduce overlapped with backward" if world > 1 else "")}
