@@ -375,14 +375,14 @@ __global__ void __launch_bounds__(128) prologue_reduce_kernel(const float *part,
     out[i] = v;
 }
 
-int check_pro(const flashmhf_prologue_params &p) {
+int check_pro(const flashmhf_prologue_params &p, bool forward) {
     if (p.B < 1 || p.S < 1 || p.H < 1 || p.E < 1 || p.E > kMaxE) return FLASHMHF_ERR_BAD_SHAPE;
     if (p.Dh != 64 && p.Dh != 96 && p.Dh != 128) return FLASHMHF_ERR_BAD_SHAPE;
     if ((long long)p.B * p.S > 0x7fffffffLL) return FLASHMHF_ERR_BAD_SHAPE;
-    if (!p.X || !p.router || !p.R) return FLASHMHF_ERR_NULL;
-    if (p.norm_weight && !p.Q) return FLASHMHF_ERR_NULL;
+    if (!p.X || !p.router) return FLASHMHF_ERR_NULL;
+    if (forward && (!p.R || (p.norm_weight && !p.Q))) return FLASHMHF_ERR_NULL;   // the backward call writes neither
     if (p.x_token_stride < (int64_t)p.H * p.Dh || (p.x_token_stride & 7)) return FLASHMHF_ERR_BAD_STRIDE;
-    if ((reinterpret_cast<uintptr_t>(p.X) & 15u) || (p.norm_weight && (reinterpret_cast<uintptr_t>(p.Q) & 15u)))
+    if ((reinterpret_cast<uintptr_t>(p.X) & 15u) || (forward && p.norm_weight && (reinterpret_cast<uintptr_t>(p.Q) & 15u)))
         return FLASHMHF_ERR_BAD_STRIDE;
     return FLASHMHF_OK;
 }
@@ -461,7 +461,7 @@ cudaError_t launch_bwd(const ProArgs &a, dim3 grid, const ProBwdArgs &g, cudaStr
 }  // namespace
 
 int prologue_forward(const flashmhf_prologue_params &p, cudaStream_t st, int *n_launch) {
-    int rc = check_pro(p);
+    int rc = check_pro(p, true);
     if (rc) return rc;
     const ProArgs a = pro_args(p);
     const dim3 grid(p.H, blocks_per_head(p, kFwdBlocksPerSM));
@@ -486,7 +486,7 @@ size_t prologue_backward_workspace_bytes(const flashmhf_prologue_params &p) {
 
 int prologue_backward(const flashmhf_prologue_bwd_params &q, cudaStream_t st, int *n_launch) {
     const flashmhf_prologue_params &p = q.fwd;
-    int rc = check_pro(p);
+    int rc = check_pro(p, false);
     if (rc) return rc;
     if (!q.dQ || !q.dR || !q.dX || !q.d_router || (p.norm_weight && !q.d_norm_weight)) return FLASHMHF_ERR_NULL;
     if ((reinterpret_cast<uintptr_t>(q.dQ) & 15u) || (reinterpret_cast<uintptr_t>(q.dX) & 15u) || (q.dq_stride[0] & 7) ||

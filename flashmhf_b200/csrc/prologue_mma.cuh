@@ -24,12 +24,25 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t saddr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+// Transposes the 8x8 matrix of bf16 that the warp holds one row-fragment register each of (lane (g,q): row g, columns 2q, 2q+1):
+// afterwards the lane holds rows 2q, 2q+1 of column g -- a row-major accumulator-style fragment becomes an operand fragment whose
+// k index is the former row index.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+    return r;
 }
-__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t (&r)[2], uint32_t saddr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(saddr));
+// Shared-memory loads the compiler must not hoist out of the tile loop: the fragments are loop-invariant, and kept in
+// registers they would cost more than a hundred of them.
+__device__ __forceinline__ uint2 lds_u2(const void *p) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(smem_u32(p)));
+    return v;
+}
+__device__ __forceinline__ float2 lds_f2(const void *p) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(smem_u32(p)));
+    return v;
 }
 __device__ __forceinline__ float quad_sum(float v) {  // over the 4 lanes that share a row
     v += __shfl_xor_sync(0xffffffffu, v, 1);
@@ -56,13 +69,9 @@ struct MmaLayout {
     static constexpr int kBf = 3 * NKS * NT * 32 * 8;        // logits B fragments: [split][ks][nt][lane] (b0, b1)
     static constexpr int kB2f = 2 * NKK * NU * 32 * 8;       // router^T B fragments: [split hi/mid][kk][u][lane]
     static constexpr int kW = DH * 4;
-    static constexpr int kYRow = DH * 2 + 16;                // padded row: ldmatrix rows fall in distinct banks
-    static constexpr int kYTile = 16 * kYRow;
-    static constexpr int kLRow = NT * 16;                    // 8 experts x bf16 per n-tile
-    static constexpr int kLTile = 3 * 16 * kLRow;            // three split terms
     static constexpr int kOffBf = 0, kOffW = kBf, kOffFwdEnd = kOffW + kW;
-    static constexpr int kOffB2f = kOffFwdEnd, kOffY = kOffB2f + kB2f, kOffL = kOffY + kWarps * kYTile,
-                         kOffBwdEnd = kOffL + kWarps * kLTile;
+    static constexpr int kWacc = 2 * NU * 32 * 4;            // per warp: d norm-weight sums of each lane's 2*NU columns, [u][j][lane]
+    static constexpr int kOffB2f = kOffFwdEnd, kOffWacc = kOffB2f + kB2f, kOffBwdEnd = kOffWacc + kWarps * kWacc;
 };
 
 // Router fragments of head h.  Bf feeds logits = y . router (k = d), B2f feeds dy += dlogits . router^T (k = e).
@@ -130,7 +139,7 @@ __device__ __forceinline__ void mma_rows_forward(MmaRows<DH, NT> &r, const ProAr
         }
 #pragma unroll
         for (int u = 0; u < L::NU; ++u) {
-            const float2 w = *reinterpret_cast<const float2 *>(wsm + mma_col(q, u));
+            const float2 w = lds_f2(wsm + mma_col(q, u));
 #pragma unroll
             for (int k = 0; k < 2; ++k)
                 r.y[k][u] = pack_bf16(bf16_lo(r.x[k][u]) * r.rstd[k] * w.x, bf16_hi(r.x[k][u]) * r.rstd[k] * w.y);
@@ -155,7 +164,7 @@ __device__ __forceinline__ void mma_rows_forward(MmaRows<DH, NT> &r, const ProAr
         for (int ks = 0; ks < L::NKS; ++ks)
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                const uint2 b = bf[((t * L::NKS + ks) * NT + nt) * 32 + lane];
+                const uint2 b = lds_u2(bf + ((t * L::NKS + ks) * NT + nt) * 32 + lane);
                 mma16816(c[nt], r.y[0][2 * ks], r.y[1][2 * ks], r.y[0][2 * ks + 1], r.y[1][2 * ks + 1], b.x, b.y);
             }
     float d0 = 0.f, d1 = 0.f;
@@ -244,13 +253,11 @@ prologue_bwd_mma_kernel(const ProArgs a, const ProBwdArgs gp) {
     float *wsm = reinterpret_cast<float *>(smem_mma + L::kOffW);
     for (int i = threadIdx.x; i < DH; i += blockDim.x) wsm[i] = NORM ? a.W[h * DH + i] : 1.f;
     __syncthreads();
-    uint8_t *ytile = smem_mma + L::kOffY + warp * L::kYTile;
-    uint8_t *ltile = smem_mma + L::kOffL + warp * L::kLTile;
-    const uint32_t ytile_s = smem_u32(ytile), ltile_s = smem_u32(ltile);
     const uint2 *b2 = reinterpret_cast<const uint2 *>(smem_mma + L::kOffB2f);
 
-    float racc[NMT][NT][4];   // d router: rows d = mt*16 + g (+8), sub-networks nt*8 + 2q + {0,1}
-    float wacc[NU][2];        // d norm weight of this lane's columns (summed over its rows)
+    float racc[NMT][NT][4];   // d router: 16 (permuted) rows d per mt, sub-networks nt*8 + 2q + {0,1}
+    // d norm weight of this lane's columns (summed over its rows): private slots in shared memory, registers are short
+    float *wacc = reinterpret_cast<float *>(smem_mma + L::kOffWacc + warp * L::kWacc) + lane;
 #pragma unroll
     for (int mt = 0; mt < NMT; ++mt)
 #pragma unroll
@@ -258,7 +265,7 @@ prologue_bwd_mma_kernel(const ProArgs a, const ProBwdArgs gp) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) racc[mt][nt][j] = 0.f;
 #pragma unroll
-    for (int u = 0; u < NU; ++u) wacc[u][0] = wacc[u][1] = 0.f;
+    for (int u = 0; u < 2 * NU; ++u) wacc[u * 32] = 0.f;
 
     for (int it = 0;; ++it) {
         const long long t0 = mma_tile_row(it, blockIdx.y, gridDim.y, warp);
@@ -287,14 +294,6 @@ prologue_bwd_mma_kernel(const ProArgs a, const ProBwdArgs gp) {
             }
         mma_rows_forward<DH, NT, NORM>(r, a, smem_mma, lane);
 
-        // y tile at its true columns for the transposed reads of the d router product
-#pragma unroll
-        for (int k = 0; k < 2; ++k)
-#pragma unroll
-            for (int i = 0; i < L::NI; ++i)
-                *reinterpret_cast<uint4 *>(ytile + (g + 8 * k) * L::kYRow + (i * 4 + q) * 16) =
-                    make_uint4(r.y[k][4 * i], r.y[k][4 * i + 1], r.y[k][4 * i + 2], r.y[k][4 * i + 3]);
-
         // R_e = sg_e / D -> dsg_e = (g_e - sum_k g_k R_k) / D ; dlogit_e = dsg_e sg_e (1 - sg_e); a clamped D passes no gradient
         float inv[2], gr[2] = {0.f, 0.f};
 #pragma unroll
@@ -305,7 +304,7 @@ prologue_bwd_mma_kernel(const ProArgs a, const ProBwdArgs gp) {
             for (int j = 0; j < 4; ++j) gr[j >> 1] = fmaf(ge[nt][j], r.sg[nt][j] * inv[j >> 1], gr[j >> 1]);
 #pragma unroll
         for (int k = 0; k < 2; ++k) gr[k] = r.D[k] > 1e-20f ? quad_sum(gr[k]) : 0.f;
-        uint32_t dlh[NT][2], dlm[NT][2];   // bf16 pairs of the hi and mid terms: [nt][row]
+        uint32_t dlh[NT][2], dlm[NT][2], dll[NT][2];   // bf16 pairs of the hi, mid and lo terms: [nt][row]
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -319,106 +318,108 @@ prologue_bwd_mma_kernel(const ProArgs a, const ProBwdArgs gp) {
                 }
                 dlh[nt][k] = pack_bf16(hi[0], hi[1]);
                 dlm[nt][k] = pack_bf16(mid[0], mid[1]);
-                const uint32_t dll = pack_bf16(lo[0], lo[1]);
-                // dlogits tile [term][row][sub-network] for the transposed reads
-                const int off = (g + 8 * k) * L::kLRow + nt * 16 + q * 4;
-                *reinterpret_cast<uint32_t *>(ltile + 0 * 16 * L::kLRow + off) = dlh[nt][k];
-                *reinterpret_cast<uint32_t *>(ltile + 1 * 16 * L::kLRow + off) = dlm[nt][k];
-                *reinterpret_cast<uint32_t *>(ltile + 2 * 16 * L::kLRow + off) = dll;
+                dll[nt][k] = pack_bf16(lo[0], lo[1]);
             }
-        __syncwarp();
 
-        // d router += y^T dlogits : 16 x 8 tiles over d (m) and sub-networks (n), k = the 16 tokens
+        // d router += y^T dlogits : 16 x 8 tiles over d (m) and sub-networks (n), k = the 16 tokens.  Both operands are
+        // transposed register fragments.  Rows of m-tile mt are the columns of y registers 2mt (m = 0..7) and 2mt+1
+        // (m = 8..15): row m stands for d = mma_col(m >> 1, u) + (m & 1).
         {
             uint32_t bfr[3][NT][2];
 #pragma unroll
-            for (int t = 0; t < 3; ++t) {
-                const uint32_t base = ltile_s + t * 16 * L::kLRow;
-                if (NT == 2) {      // matrices: (rows 0-7, nt 0) (rows 8-15, nt 0) (rows 0-7, nt 1) (rows 8-15, nt 1)
-                    uint32_t v[4];
-                    ldmatrix_x4_trans(v, base + ((lane & 7) + ((lane >> 3) & 1) * 8) * L::kLRow + (lane >> 4) * 16);
-                    bfr[t][0][0] = v[0]; bfr[t][0][1] = v[1]; bfr[t][NT - 1][0] = v[2]; bfr[t][NT - 1][1] = v[3];
-                } else {
-                    uint32_t v[2];
-                    ldmatrix_x2_trans(v, base + ((lane & 7) + ((lane >> 3) & 1) * 8) * L::kLRow);
-                    bfr[t][0][0] = v[0]; bfr[t][0][1] = v[1];
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    bfr[0][nt][k] = movmatrix_trans(dlh[nt][k]);
+                    bfr[1][nt][k] = movmatrix_trans(dlm[nt][k]);
+                    bfr[2][nt][k] = movmatrix_trans(dll[nt][k]);
                 }
-            }
 #pragma unroll
             for (int mt = 0; mt < NMT; ++mt) {
-                uint32_t av[4];     // matrices: (rows 0-7, cols c0) (rows 0-7, c0+8) (rows 8-15, c0) (rows 8-15, c0+8)
-                ldmatrix_x4_trans(av, ytile_s + ((lane & 7) + (lane >> 4) * 8) * L::kYRow + (mt * 16 + ((lane >> 3) & 1) * 8) * 2);
+                const uint32_t a0 = movmatrix_trans(r.y[0][2 * mt]), a1 = movmatrix_trans(r.y[0][2 * mt + 1]),
+                               a2 = movmatrix_trans(r.y[1][2 * mt]), a3 = movmatrix_trans(r.y[1][2 * mt + 1]);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                    for (int t = 2; t >= 0; --t) mma16816(racc[mt][nt], av[0], av[1], av[2], av[3], bfr[t][nt][0], bfr[t][nt][1]);
+                    for (int t = 2; t >= 0; --t) mma16816(racc[mt][nt], a0, a1, a2, a3, bfr[t][nt][0], bfr[t][nt][1]);
             }
         }
-        __syncwarp();   // the tiles are rewritten in the next iteration
 
-        // dy = dQ + dlogits . router^T : accumulator n-tile u holds this lane's own columns mma_col(q,u)+{0,1}
-        float dy[NU][4];
+        // dy = dQ + dlogits . router^T, n-tile u at a time (its accumulator columns are this lane's own columns
+        // mma_col(q,u)+{0,1}); evaluated twice, once for the row sums RMSNorm's backward needs and once for dx, which
+        // is cheaper than keeping d_h/2 accumulators alive.
+        auto dy_tile = [&](int u, float (&dy)[4]) {
+            dy[0] = bf16_lo(dq[0][u]); dy[1] = bf16_hi(dq[0][u]);
+            dy[2] = bf16_lo(dq[1][u]); dy[3] = bf16_hi(dq[1][u]);
 #pragma unroll
-        for (int u = 0; u < NU; ++u) {
-            dy[u][0] = bf16_lo(dq[0][u]); dy[u][1] = bf16_hi(dq[0][u]);
-            dy[u][2] = bf16_lo(dq[1][u]); dy[u][3] = bf16_hi(dq[1][u]);
-        }
-#pragma unroll
-        for (int kk = 0; kk < L::NKK; ++kk) {
-            const bool two = 2 * kk + 1 < NT;
-            const uint32_t ah0 = dlh[2 * kk][0], ah1 = dlh[2 * kk][1], ah2 = two ? dlh[two ? 2 * kk + 1 : 0][0] : 0u,
-                           ah3 = two ? dlh[two ? 2 * kk + 1 : 0][1] : 0u;
-            const uint32_t am0 = dlm[2 * kk][0], am1 = dlm[2 * kk][1], am2 = two ? dlm[two ? 2 * kk + 1 : 0][0] : 0u,
-                           am3 = two ? dlm[two ? 2 * kk + 1 : 0][1] : 0u;
-#pragma unroll
-            for (int u = 0; u < NU; ++u) {
-                const uint2 bh = b2[((0 * L::NKK + kk) * NU + u) * 32 + lane], bm = b2[((1 * L::NKK + kk) * NU + u) * 32 + lane];
-                mma16816(dy[u], am0, am1, am2, am3, bh.x, bh.y);
-                mma16816(dy[u], ah0, ah1, ah2, ah3, bm.x, bm.y);
-                mma16816(dy[u], ah0, ah1, ah2, ah3, bh.x, bh.y);
+            for (int kk = 0; kk < L::NKK; ++kk) {
+                const bool two = 2 * kk + 1 < NT;
+                const int n1 = two ? 2 * kk + 1 : 0;
+                const uint2 bh = lds_u2(b2 + ((0 * L::NKK + kk) * NU + u) * 32 + lane), bm = lds_u2(b2 + ((1 * L::NKK + kk) * NU + u) * 32 + lane);
+                mma16816(dy, dlm[2 * kk][0], dlm[2 * kk][1], two ? dlm[n1][0] : 0u, two ? dlm[n1][1] : 0u, bh.x, bh.y);
+                mma16816(dy, dlh[2 * kk][0], dlh[2 * kk][1], two ? dlh[n1][0] : 0u, two ? dlh[n1][1] : 0u, bm.x, bm.y);
+                mma16816(dy, dlh[2 * kk][0], dlh[2 * kk][1], two ? dlh[n1][0] : 0u, two ? dlh[n1][1] : 0u, bh.x, bh.y);
             }
-        }
+        };
 
         // RMSNorm backward: y_d = w_d x_d rstd ; dx_d = rstd w_d dy_d - rstd^3 x_d mean_k(w_k dy_k x_k) ; dw_d += dy_d x_d rstd
-        uint32_t dx[2][NU];
+        float r3c[2] = {0.f, 0.f};
         if (NORM) {
             float c[2] = {0.f, 0.f};
 #pragma unroll
             for (int u = 0; u < NU; ++u) {
-                const float2 w = *reinterpret_cast<const float2 *>(wsm + mma_col(q, u));
+                float dy[4];
+                dy_tile(u, dy);
+                const float2 w = lds_f2(wsm + mma_col(q, u));
+                float a0 = wacc[(2 * u) * 32], a1 = wacc[(2 * u + 1) * 32];
 #pragma unroll
                 for (int k = 0; k < 2; ++k) {
-                    const float x0 = bf16_lo(r.x[k][u]), x1 = bf16_hi(r.x[k][u]);
-                    const float p0 = dy[u][2 * k] * x0, p1 = dy[u][2 * k + 1] * x1;
+                    const float p0 = dy[2 * k] * bf16_lo(r.x[k][u]), p1 = dy[2 * k + 1] * bf16_hi(r.x[k][u]);
                     c[k] = fmaf(w.x, p0, fmaf(w.y, p1, c[k]));
-                    wacc[u][0] = fmaf(p0, r.rstd[k], wacc[u][0]);
-                    wacc[u][1] = fmaf(p1, r.rstd[k], wacc[u][1]);
+                    a0 = fmaf(p0, r.rstd[k], a0);
+                    a1 = fmaf(p1, r.rstd[k], a1);
                 }
+                wacc[(2 * u) * 32] = a0;
+                wacc[(2 * u + 1) * 32] = a1;
             }
-            float r3c[2];
 #pragma unroll
             for (int k = 0; k < 2; ++k) r3c[k] = r.rstd[k] * r.rstd[k] * r.rstd[k] * quad_sum(c[k]) * (1.f / (float)DH);
-#pragma unroll
-            for (int u = 0; u < NU; ++u) {
-                const float2 w = *reinterpret_cast<const float2 *>(wsm + mma_col(q, u));
-#pragma unroll
-                for (int k = 0; k < 2; ++k)
-                    dx[k][u] = pack_bf16(r.rstd[k] * w.x * dy[u][2 * k] - r3c[k] * bf16_lo(r.x[k][u]),
-                                         r.rstd[k] * w.y * dy[u][2 * k + 1] - r3c[k] * bf16_hi(r.x[k][u]));
-            }
-        } else {
-#pragma unroll
-            for (int u = 0; u < NU; ++u)
-#pragma unroll
-                for (int k = 0; k < 2; ++k) dx[k][u] = pack_bf16(dy[u][2 * k], dy[u][2 * k + 1]);
         }
 #pragma unroll
-        for (int k = 0; k < 2; ++k)
-            if (ok[k]) mma_store_row<DH>(gp.dX + tr[k] * a.x_tok + h * DH, dx[k], q);
+        for (int i = 0; i < L::NI; ++i) {      // one 16-byte chunk of both rows at a time, stored as soon as it is complete
+            uint32_t dx[2][4];
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                const int u = 4 * i + m;
+                float dy[4];
+                dy_tile(u, dy);
+                if (NORM) {
+                    const float2 w = lds_f2(wsm + mma_col(q, u));
+#pragma unroll
+                    for (int k = 0; k < 2; ++k)
+                        dx[k][m] = pack_bf16(r.rstd[k] * w.x * dy[2 * k] - r3c[k] * bf16_lo(r.x[k][u]),
+                                             r.rstd[k] * w.y * dy[2 * k + 1] - r3c[k] * bf16_hi(r.x[k][u]));
+                } else {
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) dx[k][m] = pack_bf16(dy[2 * k], dy[2 * k + 1]);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+                if (ok[k])
+                    reinterpret_cast<uint4 *>(gp.dX + tr[k] * a.x_tok + h * DH)[i * 4 + q] =
+                        make_uint4(dx[k][0], dx[k][1], dx[k][2], dx[k][3]);
+        }
     }
 
-    // warps' accumulators -> shared -> this block's partial sums (fixed order).  The tiles and fragments are
-    // no longer needed: the per-warp sums reuse shared memory from the start.
+    // warps' accumulators -> shared -> this block's partial sums (fixed order).  The fragments are no longer
+    // needed: the per-warp sums reuse shared memory from the start.
+    float wsum[NU][2];
+#pragma unroll
+    for (int u = 0; u < NU; ++u) {
+        wsum[u][0] = NORM ? wacc[(2 * u) * 32] : 0.f;
+        wsum[u][1] = NORM ? wacc[(2 * u + 1) * 32] : 0.f;
+    }
     __syncthreads();
     float *acc_r = reinterpret_cast<float *>(smem_mma), *acc_w = acc_r + kWarps * DE;
     float *my_r = acc_r + warp * DE, *my_w = acc_w + warp * DH;
@@ -427,15 +428,15 @@ prologue_bwd_mma_kernel(const ProArgs a, const ProBwdArgs gp) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int d = mt * 16 + g + 8 * (j >> 1), e = nt * 8 + 2 * q + (j & 1);
+            for (int j = 0; j < 4; ++j) {   // accumulator row m = g (+8): see the d router product above
+                const int d = mma_col(g >> 1, 2 * mt + (j >> 1)) + (g & 1), e = nt * 8 + 2 * q + (j & 1);
                 if (e < E) my_r[d * E + e] = racc[mt][nt][j];
             }
 #pragma unroll
     for (int u = 0; u < NU; ++u)
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            float v = wacc[u][j];   // sum over the 8 lanes that hold the same columns
+            float v = wsum[u][j];   // sum over the 8 lanes that hold the same columns
             v += __shfl_xor_sync(0xffffffffu, v, 4);
             v += __shfl_xor_sync(0xffffffffu, v, 8);
             v += __shfl_xor_sync(0xffffffffu, v, 16);

@@ -68,8 +68,6 @@ class FusedPrologueFunction(torch.autograd.Function):
                                   r.data_ptr(), None, None)
         nbytes = int(lib.flashmhf_prologue_backward_workspace_bytes(C.byref(fwd)))
         ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
-        # the C side checks Q/R only in the forward call; give it non-null placeholders
-        fwd.Q, fwd.R = x.data_ptr(), dR.data_ptr()
         p = _lib.PrologueBwdParams(fwd, dQ.data_ptr(), (C.c_int64 * 3)(*dQ.stride()[:3]), dR.data_ptr(), dX.data_ptr(),
                                    d_router.data_ptr(), d_norm.data_ptr() if ctx.has_norm else None, ws.data_ptr(), nbytes)
         with torch.cuda.device(x.device):
