@@ -44,6 +44,18 @@ __device__ __forceinline__ float2 lds_f2(const void *p) {
     asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(smem_u32(p)));
     return v;
 }
+// 16-byte asynchronous global->shared copy; `ok` false writes zeros and reads nothing.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool ok) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(ok ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint4 lds_u4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ float quad_sum(float v) {  // over the 4 lanes that share a row
     v += __shfl_xor_sync(0xffffffffu, v, 1);
     v += __shfl_xor_sync(0xffffffffu, v, 2);
@@ -71,7 +83,11 @@ struct MmaLayout {
     static constexpr int kW = DH * 4;
     static constexpr int kOffBf = 0, kOffW = kBf, kOffFwdEnd = kOffW + kW;
     static constexpr int kWacc = 2 * NU * 32 * 4;            // per warp: d norm-weight sums of each lane's 2*NU columns, [u][j][lane]
-    static constexpr int kOffB2f = kOffFwdEnd, kOffWacc = kOffB2f + kB2f, kOffBwdEnd = kOffWacc + kWarps * kWacc;
+    // per warp: two stages of {X tile, dQ tile}, 16 rows each, rows padded to DH*2 + 64 bytes so that the two rows a
+    // quarter-warp reads with one 16-byte load per lane fall into different banks
+    static constexpr int kSRow = DH * 2 + 64, kSTile = 16 * kSRow, kStage = 2 * kSTile;
+    static constexpr int kOffB2f = kOffFwdEnd, kOffWacc = kOffB2f + kB2f, kOffStage = kOffWacc + kWarps * kWacc,
+                         kOffBwdEnd = kOffStage + kWarps * 2 * kStage;
 };
 
 // Router fragments of head h.  Bf feeds logits = y . router (k = d), B2f feeds dy += dlogits . router^T (k = e).
@@ -152,11 +168,16 @@ __device__ __forceinline__ void mma_rows_forward(MmaRows<DH, NT> &r, const ProAr
             for (int u = 0; u < L::NU; ++u) r.y[k][u] = r.x[k][u];
         }
     }
-    float c[NT][4];
+    // The sum over k runs in kParts independent accumulators per n-tile so that consecutive MMAs do not wait on each
+    // other's result (a dependent MMA costs its full latency); they are added at the end.
+    constexpr int kParts = 4;
+    float cp[kParts][NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+    for (int pt = 0; pt < kParts; ++pt)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) c[nt][j] = 0.f;
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) cp[pt][nt][j] = 0.f;
     const uint2 *bf = reinterpret_cast<const uint2 *>(smem + L::kOffBf);
 #pragma unroll
     for (int t = 2; t >= 0; --t)            // smallest terms first
@@ -165,8 +186,13 @@ __device__ __forceinline__ void mma_rows_forward(MmaRows<DH, NT> &r, const ProAr
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 const uint2 b = lds_u2(bf + ((t * L::NKS + ks) * NT + nt) * 32 + lane);
-                mma16816(c[nt], r.y[0][2 * ks], r.y[1][2 * ks], r.y[0][2 * ks + 1], r.y[1][2 * ks + 1], b.x, b.y);
+                mma16816(cp[ks % kParts][nt], r.y[0][2 * ks], r.y[1][2 * ks], r.y[0][2 * ks + 1], r.y[1][2 * ks + 1], b.x, b.y);
             }
+    float c[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) c[nt][j] = (cp[0][nt][j] + cp[1][nt][j]) + (cp[2][nt][j] + cp[3][nt][j]);
     float d0 = 0.f, d1 = 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
@@ -267,30 +293,67 @@ prologue_bwd_mma_kernel(const ProArgs a, const ProBwdArgs gp) {
 #pragma unroll
     for (int u = 0; u < 2 * NU; ++u) wacc[u * 32] = 0.f;
 
+    // The next tile's X and dQ rows are copied into shared memory (cp.async, whole 256-byte rows per half-warp) while the
+    // current tile is worked on; the warp then reads them in its fragment layout, X again for each use instead of keeping it.
+    const uint32_t stage0 = smem_u32(smem_mma + L::kOffStage + warp * 2 * L::kStage);
+    auto prefetch = [&](long long t0, int buf) {
+        const uint32_t dst = stage0 + buf * L::kStage;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int row = 2 * j + (lane >> 4), cc = lane & 15;      // 16 chunks per row (d_h = 128); fewer for smaller d_h
+            if (cc * 8 < DH) {
+                const long long t = t0 + row;
+                const bool okr = t < a.T;
+                const long long b = okr ? div_by_s(t, a) : 0, sq = okr ? t - b * a.S : 0;
+                const __nv_bfloat16 *xs = okr ? a.X + t * a.x_tok + h * DH + cc * 8 : a.X;
+                const __nv_bfloat16 *qs = okr ? gp.dQ + b * gp.dq_b + (long long)h * gp.dq_h + sq * gp.dq_s + cc * 8 : gp.dQ;
+                cp_async16(dst + row * L::kSRow + cc * 16, xs, okr);
+                cp_async16(dst + L::kSTile + row * L::kSRow + cc * 16, qs, okr);
+            }
+        }
+        cp_async_commit();
+    };
+    {
+        const long long t_first = mma_tile_row(0, blockIdx.y, gridDim.y, warp);
+        if (t_first < a.T) prefetch(t_first, 0);
+    }
+
     for (int it = 0;; ++it) {
         const long long t0 = mma_tile_row(it, blockIdx.y, gridDim.y, warp);
         if (t0 >= a.T) break;
+        const long long tnext = mma_tile_row(it + 1, blockIdx.y, gridDim.y, warp);
+        if (tnext < a.T) {
+            prefetch(tnext, (it + 1) & 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncwarp();
+        const uint32_t xs = stage0 + (it & 1) * L::kStage, qs = xs + L::kSTile;
         const long long tr[2] = {t0 + g, t0 + g + 8};
         const bool ok[2] = {tr[0] < a.T, tr[1] < a.T};
-        long long roff[2];    // offset of the row's dR
-        const __nv_bfloat16 *dqp[2];
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-            const long long b = ok[k] ? div_by_s(tr[k], a) : 0, s = ok[k] ? tr[k] - b * a.S : 0;
-            roff[k] = ((b * a.H + h) * a.S + s) * E;
-            dqp[k] = gp.dQ + b * gp.dq_b + (long long)h * gp.dq_h + s * gp.dq_s;
-        }
-        MmaRows<DH, NT> r;
-        uint32_t dq[2][NU];
-        mma_load_rows<DH, NT>(r.x, a.X + tr[0] * a.x_tok + h * DH, a.X + tr[1] * a.x_tok + h * DH, ok[0], ok[1], q);
-        mma_load_rows<DH, NT>(dq, dqp[0], dqp[1], ok[0], ok[1], q);
         float ge[NT][4];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
+        for (int k = 0; k < 2; ++k) {
+            const long long b = ok[k] ? div_by_s(tr[k], a) : 0, sq = ok[k] ? tr[k] - b * a.S : 0;
+            const float *rrow = gp.dR + ((b * a.H + h) * a.S + sq) * E;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int e = nt * 8 + 2 * q + (j & 1);
-                ge[nt][j] = (ok[j >> 1] && e < E) ? __ldg(gp.dR + roff[j >> 1] + e) : 0.f;
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int e = nt * 8 + 2 * q + j;
+                    ge[nt][2 * k + j] = (ok[k] && e < E) ? __ldg(rrow + e) : 0.f;
+                }
+        }
+        // 32-bit registers 4i..4i+3 of row g + 8k of a staged tile (the chunk 4i+q of that row)
+        auto chunk = [&](uint32_t tile, int k, int i) { return lds_u4(tile + (g + 8 * k) * L::kSRow + (i * 4 + q) * 16); };
+        MmaRows<DH, NT> r;
+#pragma unroll
+        for (int k = 0; k < 2; ++k)
+#pragma unroll
+            for (int i = 0; i < L::NI; ++i) {
+                const uint4 v = chunk(xs, k, i);
+                r.x[k][4 * i] = v.x; r.x[k][4 * i + 1] = v.y; r.x[k][4 * i + 2] = v.z; r.x[k][4 * i + 3] = v.w;
             }
         mma_rows_forward<DH, NT, NORM>(r, a, smem_mma, lane);
 
@@ -335,30 +398,57 @@ prologue_bwd_mma_kernel(const ProArgs a, const ProBwdArgs gp) {
                     bfr[2][nt][k] = movmatrix_trans(dll[nt][k]);
                 }
 #pragma unroll
-            for (int mt = 0; mt < NMT; ++mt) {
-                const uint32_t a0 = movmatrix_trans(r.y[0][2 * mt]), a1 = movmatrix_trans(r.y[0][2 * mt + 1]),
-                               a2 = movmatrix_trans(r.y[1][2 * mt]), a3 = movmatrix_trans(r.y[1][2 * mt + 1]);
+            constexpr int MG = NMT % 4 == 0 ? 4 : 2;    // m-tiles per group (d_h = 96 has six)
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
+            for (int m0 = 0; m0 < NMT; m0 += MG) {      // a group of m-tiles at a time, term by term: consecutive MMAs are independent
+                uint32_t av[MG][4];
 #pragma unroll
-                    for (int t = 2; t >= 0; --t) mma16816(racc[mt][nt], a0, a1, a2, a3, bfr[t][nt][0], bfr[t][nt][1]);
+                for (int mm = 0; mm < MG; ++mm) {
+                    const int mt = m0 + mm;
+                    av[mm][0] = movmatrix_trans(r.y[0][2 * mt]);
+                    av[mm][1] = movmatrix_trans(r.y[0][2 * mt + 1]);
+                    av[mm][2] = movmatrix_trans(r.y[1][2 * mt]);
+                    av[mm][3] = movmatrix_trans(r.y[1][2 * mt + 1]);
+                }
+#pragma unroll
+                for (int t = 2; t >= 0; --t)
+#pragma unroll
+                    for (int mm = 0; mm < MG; ++mm)
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+                            mma16816(racc[m0 + mm][nt], av[mm][0], av[mm][1], av[mm][2], av[mm][3], bfr[t][nt][0], bfr[t][nt][1]);
             }
         }
 
         // dy = dQ + dlogits . router^T, n-tile u at a time (its accumulator columns are this lane's own columns
         // mma_col(q,u)+{0,1}); evaluated twice, once for the row sums RMSNorm's backward needs and once for dx, which
         // is cheaper than keeping d_h/2 accumulators alive.
-        auto dy_tile = [&](int u, float (&dy)[4]) {
-            dy[0] = bf16_lo(dq[0][u]); dy[1] = bf16_hi(dq[0][u]);
-            dy[2] = bf16_lo(dq[1][u]); dy[3] = bf16_hi(dq[1][u]);
+        auto word = [](const uint4 &v, int m) { return m == 0 ? v.x : m == 1 ? v.y : m == 2 ? v.z : v.w; };
+        auto dy_chunk = [&](int i, const uint4 &q0, const uint4 &q1, float (&dy)[4][4]) {   // n-tiles 4i .. 4i+3, term by term
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                dy[m][0] = bf16_lo(word(q0, m)); dy[m][1] = bf16_hi(word(q0, m));
+                dy[m][2] = bf16_lo(word(q1, m)); dy[m][3] = bf16_hi(word(q1, m));
+            }
 #pragma unroll
             for (int kk = 0; kk < L::NKK; ++kk) {
                 const bool two = 2 * kk + 1 < NT;
                 const int n1 = two ? 2 * kk + 1 : 0;
-                const uint2 bh = lds_u2(b2 + ((0 * L::NKK + kk) * NU + u) * 32 + lane), bm = lds_u2(b2 + ((1 * L::NKK + kk) * NU + u) * 32 + lane);
-                mma16816(dy, dlm[2 * kk][0], dlm[2 * kk][1], two ? dlm[n1][0] : 0u, two ? dlm[n1][1] : 0u, bh.x, bh.y);
-                mma16816(dy, dlh[2 * kk][0], dlh[2 * kk][1], two ? dlh[n1][0] : 0u, two ? dlh[n1][1] : 0u, bm.x, bm.y);
-                mma16816(dy, dlh[2 * kk][0], dlh[2 * kk][1], two ? dlh[n1][0] : 0u, two ? dlh[n1][1] : 0u, bh.x, bh.y);
+                uint2 bh[4], bm[4];
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    bh[m] = lds_u2(b2 + ((0 * L::NKK + kk) * NU + 4 * i + m) * 32 + lane);
+                    bm[m] = lds_u2(b2 + ((1 * L::NKK + kk) * NU + 4 * i + m) * 32 + lane);
+                }
+#pragma unroll
+                for (int m = 0; m < 4; ++m)
+                    mma16816(dy[m], dlm[2 * kk][0], dlm[2 * kk][1], two ? dlm[n1][0] : 0u, two ? dlm[n1][1] : 0u, bh[m].x, bh[m].y);
+#pragma unroll
+                for (int m = 0; m < 4; ++m)
+                    mma16816(dy[m], dlh[2 * kk][0], dlh[2 * kk][1], two ? dlh[n1][0] : 0u, two ? dlh[n1][1] : 0u, bm[m].x, bm[m].y);
+#pragma unroll
+                for (int m = 0; m < 4; ++m)
+                    mma16816(dy[m], dlh[2 * kk][0], dlh[2 * kk][1], two ? dlh[n1][0] : 0u, two ? dlh[n1][1] : 0u, bh[m].x, bh[m].y);
             }
         };
 
@@ -367,38 +457,48 @@ prologue_bwd_mma_kernel(const ProArgs a, const ProBwdArgs gp) {
         if (NORM) {
             float c[2] = {0.f, 0.f};
 #pragma unroll
-            for (int u = 0; u < NU; ++u) {
-                float dy[4];
-                dy_tile(u, dy);
-                const float2 w = lds_f2(wsm + mma_col(q, u));
-                float a0 = wacc[(2 * u) * 32], a1 = wacc[(2 * u + 1) * 32];
+            for (int i = 0; i < L::NI; ++i) {
+                const uint4 x0 = chunk(xs, 0, i), x1 = chunk(xs, 1, i), q0 = chunk(qs, 0, i), q1 = chunk(qs, 1, i);
+                float dy4[4][4];
+                dy_chunk(i, q0, q1, dy4);
 #pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    const float p0 = dy[2 * k] * bf16_lo(r.x[k][u]), p1 = dy[2 * k + 1] * bf16_hi(r.x[k][u]);
-                    c[k] = fmaf(w.x, p0, fmaf(w.y, p1, c[k]));
-                    a0 = fmaf(p0, r.rstd[k], a0);
-                    a1 = fmaf(p1, r.rstd[k], a1);
+                for (int m = 0; m < 4; ++m) {
+                    const int u = 4 * i + m;
+                    const float(&dy)[4] = dy4[m];
+                    const float2 w = lds_f2(wsm + mma_col(q, u));
+                    const uint32_t xw[2] = {word(x0, m), word(x1, m)};
+                    float a0 = wacc[(2 * u) * 32], a1 = wacc[(2 * u + 1) * 32];
+#pragma unroll
+                    for (int k = 0; k < 2; ++k) {
+                        const float p0 = dy[2 * k] * bf16_lo(xw[k]), p1 = dy[2 * k + 1] * bf16_hi(xw[k]);
+                        c[k] = fmaf(w.x, p0, fmaf(w.y, p1, c[k]));
+                        a0 = fmaf(p0, r.rstd[k], a0);
+                        a1 = fmaf(p1, r.rstd[k], a1);
+                    }
+                    wacc[(2 * u) * 32] = a0;
+                    wacc[(2 * u + 1) * 32] = a1;
                 }
-                wacc[(2 * u) * 32] = a0;
-                wacc[(2 * u + 1) * 32] = a1;
             }
 #pragma unroll
             for (int k = 0; k < 2; ++k) r3c[k] = r.rstd[k] * r.rstd[k] * r.rstd[k] * quad_sum(c[k]) * (1.f / (float)DH);
         }
 #pragma unroll
         for (int i = 0; i < L::NI; ++i) {      // one 16-byte chunk of both rows at a time, stored as soon as it is complete
+            const uint4 x0 = chunk(xs, 0, i), x1 = chunk(xs, 1, i), q0 = chunk(qs, 0, i), q1 = chunk(qs, 1, i);
             uint32_t dx[2][4];
+            float dy4[4][4];
+            dy_chunk(i, q0, q1, dy4);
 #pragma unroll
             for (int m = 0; m < 4; ++m) {
                 const int u = 4 * i + m;
-                float dy[4];
-                dy_tile(u, dy);
+                const float(&dy)[4] = dy4[m];
                 if (NORM) {
                     const float2 w = lds_f2(wsm + mma_col(q, u));
+                    const uint32_t xw[2] = {word(x0, m), word(x1, m)};
 #pragma unroll
                     for (int k = 0; k < 2; ++k)
-                        dx[k][m] = pack_bf16(r.rstd[k] * w.x * dy[2 * k] - r3c[k] * bf16_lo(r.x[k][u]),
-                                             r.rstd[k] * w.y * dy[2 * k + 1] - r3c[k] * bf16_hi(r.x[k][u]));
+                        dx[k][m] = pack_bf16(r.rstd[k] * w.x * dy[2 * k] - r3c[k] * bf16_lo(xw[k]),
+                                             r.rstd[k] * w.y * dy[2 * k + 1] - r3c[k] * bf16_hi(xw[k]));
                 } else {
 #pragma unroll
                     for (int k = 0; k < 2; ++k) dx[k][m] = pack_bf16(dy[2 * k], dy[2 * k + 1]);
@@ -410,6 +510,7 @@ prologue_bwd_mma_kernel(const ProArgs a, const ProBwdArgs gp) {
                     reinterpret_cast<uint4 *>(gp.dX + tr[k] * a.x_tok + h * DH)[i * 4 + q] =
                         make_uint4(dx[k][0], dx[k][1], dx[k][2], dx[k][3]);
         }
+        __syncwarp();   // every lane is done with this stage before the copy of the tile after next overwrites it
     }
 
     // warps' accumulators -> shared -> this block's partial sums (fixed order).  The fragments are no longer
