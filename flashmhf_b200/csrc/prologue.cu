@@ -11,16 +11,17 @@
 //
 // and its backward (dQ and dR from the operator -> dX, d router, d w), recomputing the forward from X.
 //
-// Both are HBM-bound streaming kernels on the CUDA cores.  One warp owns one (token, head) row at a
-// time: lane l holds the d_h/32 consecutive elements d = l*d_h/32 .. (one 8-byte load per lane for
-// d_h = 128, so a row is one fully coalesced 256-byte request).  A block serves one head, so each lane
-// keeps its slice of that head's router matrix (and, in the backward, of its gradient) in registers
-// for the whole block; the per-row work is then a few dozen FMAs and shuffles.  The grid is persistent
-// (heads x about one or two blocks per SM): a block loads its head's router matrix once, through shared
-// memory, and then its warps take row pairs round-robin until the tokens run out, the next pair's loads
-// issued before the current pair's arithmetic, which is what hides the DRAM latency at this occupancy.
-// Weight gradients leave the block as per-block partial sums and are added over blocks by a second
-// kernel in a fixed order (no floating-point atomics, so results are bit-reproducible).
+// Both are HBM-bound streaming kernels.  Two families share this file's host code:
+//   * up to 16 sub-networks per head (the shipped configurations): prologue_mma.cuh -- 16-token tiles per
+//     warp, the three small products as warp-level MMA tiles;
+//   * 17..32 sub-networks: the kernels below -- one warp owns one (token, head) row at a time, lane l
+//     holds the d_h/32 consecutive elements d = l*d_h/32 .. (one 8-byte load per lane for d_h = 128), the
+//     head's router matrix sits re-ordered in shared memory, the logits are reduced across lanes with a
+//     transposing butterfly, and the backward keeps its share of d router in registers.
+// In both, a block serves one head on a persistent grid (heads x about one or two blocks per SM), loads
+// its head's router matrix once and deals tokens to its warps round-robin.  Weight gradients leave the
+// block as per-block partial sums and are added over blocks by a second kernel in a fixed order (no
+// floating-point atomics, so results are bit-reproducible).
 #include "kernels.h"
 #include "tc_common.cuh"
 
@@ -117,42 +118,28 @@ __device__ __forceinline__ void store_row(__nv_bfloat16 *row, int lane, const fl
 }
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16(v)); }
 
-// The router slice of one lane: router[h, lane*EPL + i, e].  In registers for EP <= 16; for more
-// sub-networks in shared memory as [e][i][lane] (conflict-free), because the backward also keeps an
-// accumulator of the same shape in registers.
+// The router slice of one lane, router[h, lane*EPL + i, e], in shared memory as [e][i][lane] (conflict-free):
+// these kernels serve 17..32 sub-networks, where a register copy next to the backward's same-shaped accumulator
+// would not fit (up to 16 sub-networks run the MMA kernels of prologue_mma.cuh).
 template <int EPL, int EP>
 struct RouterSlice {
-    static constexpr bool kRegs = EP <= 16;
-    float reg[kRegs ? EPL : 1][kRegs ? EP : 1];
     const float *sm;
     int lane;
-    // Stages router[h] (Dh*E floats) in shared memory with coalesced loads; then either copies this lane's
-    // slice to registers or leaves it there re-ordered.  `stage` needs Dh*E floats (2*Dh*E when !kRegs).
+    // Stages router[h] (Dh*E floats) in shared memory with coalesced loads, then re-orders it.  `stage`: 2*Dh*E floats.
     __device__ __forceinline__ void init(const float *router_h, float *stage, int E, int lane_) {
         lane = lane_;
         const int n = EPL * 32 * E;
         for (int k = threadIdx.x; k < n; k += blockDim.x) stage[k] = router_h[k];
         __syncthreads();
-        if constexpr (kRegs) {
-            sm = stage;
-#pragma unroll
-            for (int i = 0; i < EPL; ++i)
-#pragma unroll
-                for (int e = 0; e < EP; ++e) reg[i][e] = e < E ? stage[(lane * EPL + i) * E + e] : 0.f;
-        } else {
-            float *dst = stage + n;
-            for (int k = threadIdx.x; k < n; k += blockDim.x) {
-                const int d = k / E, e = k - d * E;  // d = l*EPL + i
-                dst[(e * EPL + d % EPL) * 32 + d / EPL] = stage[k];
-            }
-            sm = dst;
+        float *dst = stage + n;
+        for (int k = threadIdx.x; k < n; k += blockDim.x) {
+            const int d = k / E, e = k - d * E;  // d = l*EPL + i
+            dst[(e * EPL + d % EPL) * 32 + d / EPL] = stage[k];
         }
+        sm = dst;
         __syncthreads();
     }
-    __device__ __forceinline__ float at(int i, int e) const {
-        if constexpr (kRegs) return reg[i][e];
-        else return sm[(e * EPL + i) * 32 + lane];
-    }
+    __device__ __forceinline__ float at(int i, int e) const { return sm[(e * EPL + i) * 32 + lane]; }
 };
 
 template <int EPL>
@@ -249,10 +236,10 @@ prologue_bwd_kernel(const ProArgs a, const ProBwdArgs g) {
     constexpr int EPL = DH / 32;
     extern __shared__ float sm[];
     const int E = a.E, DE = DH * E;
-    // shared: [router staging: DE, twice that when the slice stays in shared memory]
+    // shared: [router staging and re-ordered copy: 2*DE]
     //         [per-warp d router: kWarps*DE] [per-warp d w: kWarps*DH]
     float *router_s = sm;
-    float *acc_r = sm + (RouterSlice<EPL, EP>::kRegs ? DE : 2 * DE), *acc_w = acc_r + kWarps * DE;
+    float *acc_r = sm + 2 * DE, *acc_w = acc_r + kWarps * DE;
     const int h = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     RouterSlice<EPL, EP> rt;
     rt.init(a.router + (long long)h * DE, router_s, E, lane);
@@ -405,7 +392,7 @@ int blocks_per_head(const flashmhf_prologue_params &p, int per_sm) {
     return (int)(want < most ? want : most);
 }
 
-size_t fwd_smem(int DH, int EP, int E) { return (size_t)(EP <= 16 ? 1 : 2) * DH * E * sizeof(float); }
+size_t fwd_smem(int DH, int EP, int E) { return (size_t)2 * DH * E * sizeof(float); }
 size_t bwd_smem(int DH, int EP, int E) {
     return fwd_smem(DH, EP, E) + (size_t)kWarps * ((size_t)DH * E + DH) * sizeof(float);
 }
@@ -427,7 +414,7 @@ cudaError_t launch_bwd(const ProArgs &a, dim3 grid, const ProBwdArgs &g, cudaStr
     return cudaGetLastError();
 }
 
-// dispatch on (d_h, sub-network count rounded up to 16 or 32, RMSNorm on/off)
+// dispatch on (d_h, n-tiles of 8 sub-networks, RMSNorm on/off); the per-lane kernels below it serve E > 16
 #define FMHF_PRO_DISPATCH_MMA(CALL)                                                        \
     do {                                                                                   \
         const bool norm = p.norm_weight != nullptr, one = p.E <= 8;                        \
@@ -445,17 +432,10 @@ cudaError_t launch_bwd(const ProArgs &a, dim3 grid, const ProBwdArgs &g, cudaStr
 
 #define FMHF_PRO_DISPATCH(CALL)                                                            \
     do {                                                                                   \
-        const bool norm = p.norm_weight != nullptr, small = p.E <= 16;                     \
-        if (p.Dh == 128) {                                                                 \
-            if (small) { if (norm) e = CALL(128, 16, true); else e = CALL(128, 16, false); } \
-            else       { if (norm) e = CALL(128, 32, true); else e = CALL(128, 32, false); } \
-        } else if (p.Dh == 96) {                                                           \
-            if (small) { if (norm) e = CALL(96, 16, true); else e = CALL(96, 16, false); }   \
-            else       { if (norm) e = CALL(96, 32, true); else e = CALL(96, 32, false); }   \
-        } else {                                                                           \
-            if (small) { if (norm) e = CALL(64, 16, true); else e = CALL(64, 16, false); }   \
-            else       { if (norm) e = CALL(64, 32, true); else e = CALL(64, 32, false); }   \
-        }                                                                                  \
+        const bool norm = p.norm_weight != nullptr;                                        \
+        if (p.Dh == 128) { if (norm) e = CALL(128, 32, true); else e = CALL(128, 32, false); } \
+        else if (p.Dh == 96) { if (norm) e = CALL(96, 32, true); else e = CALL(96, 32, false); } \
+        else { if (norm) e = CALL(64, 32, true); else e = CALL(64, 32, false); }            \
     } while (0)
 
 }  // namespace
