@@ -302,6 +302,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             for (int sub = 0; sub < 2; ++sub) {
                 uint32_t m[16], n[16], da[16];
                 tmem_ld16x3_sync(tS + sub * 16, tS + kBI + sub * 16, tS + kColdA + sub * 16, m, n, da);
+                if (sub == 1) {   // S is in registers: it may be recomputed for block j+2 from here on
+                    tc_fence_before();
+                    mbar_arrive(bar(DQ_SEMPTY + bb));
+                }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const BwdPair x = bwd_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]), f2_pack_bits(n[2 * i], n[2 * i + 1]),
@@ -311,8 +315,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     pn[sub * 8 + i] = f2_to_bf16x2(x.dn);
                 }
             }
-            tc_fence_before();
-            mbar_arrive(bar(DQ_SEMPTY + bb));  // S may be recomputed for block j+2 from here on
             // dM and dN go back into tensor memory as packed bf16 pairs, over the 32 dA columns this
             // thread has just read (no other thread reads those columns)
             tmem_st16(tS + kColdA, pm);
