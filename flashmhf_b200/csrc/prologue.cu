@@ -12,9 +12,9 @@
 // and its backward (dQ and dR from the operator -> dX, d router, d w), recomputing the forward from X.
 //
 // Both are HBM-bound streaming kernels.  Two families share this file's host code:
-//   * up to 16 sub-networks per head (the shipped configurations): prologue_mma.cuh -- 16-token tiles per
+//   * up to 24 sub-networks per head (the shipped configurations have 8, 11 and 22): prologue_mma.cuh -- 16-token tiles per
 //     warp, the three small products as warp-level MMA tiles;
-//   * 17..32 sub-networks: the kernels below -- one warp owns one (token, head) row at a time, lane l
+//   * 25..32 sub-networks: the kernels below -- one warp owns one (token, head) row at a time, lane l
 //     holds the d_h/32 consecutive elements d = l*d_h/32 .. (one 8-byte load per lane for d_h = 128), the
 //     head's router matrix sits re-ordered in shared memory, the logits are reduced across lanes with a
 //     transposing butterfly, and the backward keeps its share of d router in registers.
@@ -119,8 +119,8 @@ __device__ __forceinline__ void store_row(__nv_bfloat16 *row, int lane, const fl
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16(v)); }
 
 // The router slice of one lane, router[h, lane*EPL + i, e], in shared memory as [e][i][lane] (conflict-free):
-// these kernels serve 17..32 sub-networks, where a register copy next to the backward's same-shaped accumulator
-// would not fit (up to 16 sub-networks run the MMA kernels of prologue_mma.cuh).
+// these kernels serve 25..32 sub-networks, where a register copy next to the backward's same-shaped accumulator
+// would not fit (up to 24 sub-networks run the MMA kernels of prologue_mma.cuh).
 template <int EPL, int EP>
 struct RouterSlice {
     const float *sm;
@@ -381,8 +381,9 @@ ProArgs pro_args(const flashmhf_prologue_params &p) {
     return ProArgs{static_cast<const __nv_bfloat16 *>(p.X), p.x_token_stride, p.norm_weight, p.router, p.eps,
                    p.B * p.S, p.H, p.E, p.S, mul, 31 + l};
 }
-// E <= 16 runs the MMA kernels (16-token tiles per warp), more sub-networks the per-lane kernels (row pairs).
-bool use_mma(const flashmhf_prologue_params &p) { return p.E <= 16; }
+// E <= 24 runs the MMA kernels (16-token tiles per warp; the backward's d-router accumulator takes 32 registers per
+// 8 sub-networks), more sub-networks the per-lane kernels (row pairs).
+bool use_mma(const flashmhf_prologue_params &p) { return p.E <= 24; }
 
 // Blocks per head: enough to fill the GPU `per_sm` times over, never more than there are warp work items to deal.
 int blocks_per_head(const flashmhf_prologue_params &p, int per_sm) {
@@ -414,20 +415,19 @@ cudaError_t launch_bwd(const ProArgs &a, dim3 grid, const ProBwdArgs &g, cudaStr
     return cudaGetLastError();
 }
 
-// dispatch on (d_h, n-tiles of 8 sub-networks, RMSNorm on/off); the per-lane kernels below it serve E > 16
+// dispatch on (d_h, n-tiles of 8 sub-networks, RMSNorm on/off); the per-lane kernels below it serve E > 24
+#define FMHF_PRO_DISPATCH_MMA_DH(CALL, DH)                                                  \
+    do {                                                                                   \
+        const bool norm = p.norm_weight != nullptr;                                        \
+        if (p.E <= 8) { if (norm) e = CALL(DH, 1, true); else e = CALL(DH, 1, false); }     \
+        else if (p.E <= 16) { if (norm) e = CALL(DH, 2, true); else e = CALL(DH, 2, false); } \
+        else { if (norm) e = CALL(DH, 3, true); else e = CALL(DH, 3, false); }              \
+    } while (0)
 #define FMHF_PRO_DISPATCH_MMA(CALL)                                                        \
     do {                                                                                   \
-        const bool norm = p.norm_weight != nullptr, one = p.E <= 8;                        \
-        if (p.Dh == 128) {                                                                 \
-            if (one) { if (norm) e = CALL(128, 1, true); else e = CALL(128, 1, false); }   \
-            else     { if (norm) e = CALL(128, 2, true); else e = CALL(128, 2, false); }   \
-        } else if (p.Dh == 96) {                                                           \
-            if (one) { if (norm) e = CALL(96, 1, true); else e = CALL(96, 1, false); }     \
-            else     { if (norm) e = CALL(96, 2, true); else e = CALL(96, 2, false); }     \
-        } else {                                                                           \
-            if (one) { if (norm) e = CALL(64, 1, true); else e = CALL(64, 1, false); }     \
-            else     { if (norm) e = CALL(64, 2, true); else e = CALL(64, 2, false); }     \
-        }                                                                                  \
+        if (p.Dh == 128) FMHF_PRO_DISPATCH_MMA_DH(CALL, 128);                              \
+        else if (p.Dh == 96) FMHF_PRO_DISPATCH_MMA_DH(CALL, 96);                           \
+        else FMHF_PRO_DISPATCH_MMA_DH(CALL, 64);                                           \
     } while (0)
 
 #define FMHF_PRO_DISPATCH(CALL)                                                            \

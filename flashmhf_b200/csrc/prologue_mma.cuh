@@ -1,4 +1,4 @@
-// Prologue kernels for up to 16 sub-networks per head: the three small products of the prologue
+// Prologue kernels for up to 24 sub-networks per head: the three small products of the prologue
 //   logits[t,e]    = sum_d y[t,d] router[d,e]                     (forward, and recomputed in backward)
 //   dy[t,d]       += sum_e dlogits[t,e] router[d,e]
 //   d router[d,e] += sum_t y[t,d] dlogits[t,e]
@@ -397,7 +397,6 @@ prologue_bwd_mma_kernel(const ProArgs a, const ProBwdArgs gp) {
                     bfr[1][nt][k] = movmatrix_trans(dlm[nt][k]);
                     bfr[2][nt][k] = movmatrix_trans(dll[nt][k]);
                 }
-#pragma unroll
             constexpr int MG = NMT % 4 == 0 ? 4 : 2;    // m-tiles per group (d_h = 96 has six)
 #pragma unroll
             for (int m0 = 0; m0 < NMT; m0 += MG) {      // a group of m-tiles at a time, term by term: consecutive MMAs are independent

@@ -14,7 +14,8 @@ pytestmark = pytest.mark.gpu
 
 # (B, S, H, d_h, E, rmsnorm)
 CASES = [(2, 100, 3, 64, 4, True), (1, 257, 2, 96, 1, True), (3, 128, 4, 128, 11, True),
-         (2, 77, 2, 128, 32, True), (2, 130, 3, 64, 5, False), (1, 1, 2, 128, 7, True), (4, 512, 8, 128, 11, True)]
+         (2, 77, 2, 128, 32, True), (2, 130, 3, 64, 5, False), (1, 1, 2, 128, 7, True), (4, 512, 8, 128, 11, True),
+         (2, 150, 4, 128, 22, True), (1, 90, 2, 96, 17, True), (2, 40, 2, 64, 24, False), (1, 70, 2, 128, 25, True)]
 
 
 def _inputs(B, S, H, dh, E, seed):
