@@ -108,7 +108,10 @@ def backward_raw(Q, K, U, V, R, dO):
     if R.stride(-1) != 1:
         R = R.contiguous()
     dQ = torch.empty_like(Q)  # keeps Q's memory layout
-    dK, dU, dV = (torch.empty_like(t, memory_format=torch.contiguous_format) for t in (K, U, V))
+    # weight gradients in the weights' own memory layout (the layer passes strided views of [I, H_kuv*d_h] parameters:
+    # their gradients then need no re-layout copy); the fp32 check kernels write contiguous outputs
+    fmt = torch.preserve_format if Q.dtype == torch.bfloat16 else torch.contiguous_format
+    dK, dU, dV = (torch.empty_like(t, memory_format=fmt) for t in (K, U, V))
     dR = torch.empty((B, H, S, E), dtype=torch.float32, device=Q.device)
     d = _dims(B, H, S, dh, hk, E, de, Q.dtype)
     nbytes = int(lib.flashmhf_backward_workspace_bytes(C.byref(d)))
