@@ -39,6 +39,6 @@ def test_clock_sampler_parses_nvidia_smi_lines():
                "garbage line", "[N/A], 1965, 1.0, Not Active, Not Active, Not Active, Not Active"]
     r = s.stop()
     assert r["sm_mhz"] == 1680.0 and r["sm_max_mhz"] == 1965.0 and r["samples"] == 3
-    assert r["reasons"] == ["sw_power_cap"]
+    assert r["reasons"] == ["sw_power_cap"] and r["power_w"] == 998.1
     s2 = b.ClockSampler(0)
     assert s2.stop()["sm_mhz"] is None                             # never started: reported as unavailable, not as zero
