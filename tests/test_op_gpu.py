@@ -216,3 +216,52 @@ def test_forward_and_backward_replay_from_a_cuda_graph():
         for a, b in zip(got, want):
             assert torch.equal(a, b)
         _lib.device_status()
+
+
+def test_autograd_under_activation_checkpointing():
+    """The function saves only its inputs and recomputes, so it must behave under torch.utils.checkpoint (re-entrant
+    forward inside backward) exactly as without it."""
+    import flashmhf_b200 as fm
+    from torch.utils.checkpoint import checkpoint
+    Q, K, U, V, R, dO = (t.cuda() for t in orc.make_op_inputs(2, 2, 150, 128, 2, 64, seed=91, dtype=torch.bfloat16))
+
+    def run(use_ckpt):
+        ins = [t.detach().clone().requires_grad_(True) for t in (Q, K, U, V, R)]
+        O = checkpoint(fm.flash_mhf, *ins, use_reentrant=False) if use_ckpt else fm.flash_mhf(*ins)
+        O.backward(dO)
+        return [O.detach()] + [t.grad for t in ins]
+
+    for a, b in zip(run(False), run(True)):
+        assert torch.equal(a, b)
+
+
+def test_two_host_threads_on_their_own_streams():
+    """The library keeps no per-call state: two host threads, each on its own stream with its own inputs, get the
+    results a single thread gets."""
+    import threading
+    import flashmhf_b200 as fm
+    sets = [[t.cuda() for t in orc.make_op_inputs(1, 2, 260, 128, 2, 128, seed=s, dtype=torch.bfloat16)] for s in (5, 6)]
+    want = [[fm.forward_raw(*d[:5])] + list(fm.backward_raw(*d)) for d in sets]
+    torch.cuda.synchronize()
+    got, errs = [None, None], []
+
+    def work(i):
+        try:
+            st = torch.cuda.Stream()
+            with torch.cuda.stream(st):
+                for _ in range(20):
+                    r = [fm.forward_raw(*sets[i][:5])] + list(fm.backward_raw(*sets[i]))
+            st.synchronize()
+            got[i] = r
+        except Exception as e:  # surfaced in the main thread below
+            errs.append(e)
+
+    ths = [threading.Thread(target=work, args=(i,)) for i in range(2)]
+    for t in ths:
+        t.start()
+    for t in ths:
+        t.join()
+    assert not errs, errs
+    for i in range(2):
+        for a, b in zip(got[i], want[i]):
+            assert torch.equal(a, b)
