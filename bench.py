@@ -172,6 +172,22 @@ def run_reference(args, rank, world):
     }))
 
 
+def bind_to_gpu_numa_node(index):
+    """Run this process on the CPUs next to its GPU, so that the pinned host buffers of the end-to-end leg are allocated
+    on that NUMA node and their copies do not cross the socket interconnect.  Best effort: silently skipped without NVML."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (w >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+    except Exception:
+        pass
+
+
 def lm_train_370m(args, rank, world, dev, sync_all):
     """The second half of the headline metric: full training steps (forward, backward, gradient all-reduce,
     AdamW) of the 370M decoder LM at batch 16 x 2048 per GPU, bf16, uniform random token ids, data-parallel.
@@ -238,6 +254,8 @@ def main():
     import flashmhf_b200 as fm
     from flashmhf_b200 import _lib, dp
     _lib.load()  # fails loudly if the CUDA library is missing
+    if world > 1:   # one rank per GPU shares the host: keep each rank's pinned buffers on its GPU's NUMA node
+        bind_to_gpu_numa_node(local_rank)
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist = None
