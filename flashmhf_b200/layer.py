@@ -79,6 +79,20 @@ def fused_prologue(x_proj, q_norm, router, eps=1e-5):
     return FusedPrologueFunction.apply(x_proj, q_norm, router, eps)
 
 
+def torch_prologue(x_proj, q_norm, router, eps=1e-5):
+    """The same two results from library element-wise kernels, for router shapes the fused kernels do not take (more
+    than 32 sub-networks per head): per-head RMSNorm in fp32, Q as a [B,H,S,d_h] view, R = normalised sigmoid."""
+    H, dh, _ = router.shape
+    B, S, _ = x_proj.shape
+    q = x_proj.view(B, S, H, dh)
+    if q_norm is not None:
+        qf = q.float()
+        q = (qf * torch.rsqrt(qf.pow(2).mean(-1, keepdim=True) + eps) * q_norm.float()[None, None]).to(x_proj.dtype)
+    Q = q.transpose(1, 2)
+    R = (Q.float() @ router.float()).sigmoid()
+    return Q, R / R.sum(dim=-1, keepdim=True).clamp(min=1e-20)
+
+
 def expert_views(gate_weight, up_weight, down_weight, Hkuv, E):
     """[I, H_kuv*d_h] parameters -> [H_kuv, E, d_e, d_h] strided views the operator reads in place (no copy)."""
     I = gate_weight.shape[0]
@@ -91,7 +105,8 @@ def mhffn_layer(x, p, *, H, Hkuv, E, apply_rmsnorm, eps=1e-5):
     """y = w_self_2(op(prologue(w_self(x)))) for bf16 CUDA tensors; p holds the reference's parameter names."""
     B, S, hid = x.shape
     q_lin = F.linear(x, p["w_self"]) if p.get("w_self") is not None else x
-    Q, R = fused_prologue(q_lin, p["q_norm"] if apply_rmsnorm else None, p["router"], eps)
+    prologue = fused_prologue if E <= 32 else torch_prologue
+    Q, R = prologue(q_lin, p["q_norm"] if apply_rmsnorm else None, p["router"], eps)
     K, U, V = expert_views(p["gate_weight"], p["up_weight"], p["down_weight"], Hkuv, E)
     O = flash_mhf(Q, K, U, V, R)                      # [B,H,S,d_h] view of [B,S,H,d_h] memory
     O = O.transpose(1, 2).reshape(B, S, hid)          # no copy when O kept Q's layout

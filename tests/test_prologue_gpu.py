@@ -145,3 +145,28 @@ def test_fused_layer_equals_unfused_layer_on_gpu():
     a = orc.mhffn_layer_forward(x, pf, op=fm.flash_mhf, **kw)
     b = fm.mhffn_layer(x, p, **kw)
     assert orc.rel_l2(b.float().cpu(), a.float().cpu()) < 5e-3
+
+
+def test_layer_with_more_sub_networks_than_the_fused_prologue_takes():
+    """E = 40 > 32: the layer keeps working through torch's element-wise kernels for the prologue; the operator itself
+    has no limit on E."""
+    import flashmhf_b200 as fm
+    g = torch.Generator().manual_seed(9)
+    hid, H, E, de = 128, 2, 40, 64
+    p = {"w_self": torch.randn(hid, hid, generator=g) * 0.05, "w_self_2": torch.randn(hid, hid, generator=g) * 0.05,
+         "gate_weight": torch.randn(E * de, hid, generator=g) * 0.05, "up_weight": torch.randn(E * de, hid, generator=g) * 0.05,
+         "down_weight": torch.randn(E * de, hid, generator=g) * 0.05, "router": torch.randn(H, hid // H, E, generator=g) * 0.2,
+         "q_norm": 1.0 + 0.1 * torch.randn(H, hid // H, generator=g)}
+    x = torch.randn(2, 50, hid, generator=g)
+    kw = dict(H=H, Hkuv=H, E=E, apply_rmsnorm=True, eps=1e-5)
+    pc = {k: v.cuda().bfloat16().requires_grad_(True) for k, v in p.items()}
+    xc = x.cuda().bfloat16().requires_grad_(True)
+    y = fm.mhffn_layer(xc, pc, **kw)
+    y.float().sum().backward()
+    po = {k: v.clone().requires_grad_(True) for k, v in p.items()}
+    xo = x.clone().requires_grad_(True)
+    yo = orc.mhffn_layer_forward(xo, po, **kw)
+    yo.sum().backward()
+    assert orc.rel_l2(y.float().cpu(), yo) < 2e-2
+    assert orc.rel_l2(xc.grad.float().cpu(), xo.grad) < 3e-2
+    assert orc.rel_l2(pc["router"].grad.float().cpu(), po["router"].grad) < 5e-2
