@@ -5,14 +5,18 @@
 One step = one forward and one backward pass of the operator over one batch of synthetic input
 (per GPU: B=16 x S=2048 tokens, H=8 heads of d_h=128, E=11 sub-networks of d_e=256 -- the FFN of one
 layer of the 370M configuration).  With N > 1 (one process per GPU, launched by torch.distributed.run)
-every rank works on its own batch with replicated weights and the step ends with one NCCL all-reduce
-of dK, dU, dV (data-parallel training's only exchange); scaling is weak.
+every rank works on its own batch with replicated weights and the step holds one NCCL all-reduce of
+dK, dU, dV (data-parallel training's only exchange), started as soon as the weight gradients exist and
+running under the dQ/dR kernel; scaling is weak.
 
 The metric is algorithmic TFLOP/s: 18*T*H*I*d_h FLOPs per step (3 forward + 6 gradient GEMMs; the
 recomputation the backward needs is NOT counted) divided by the step time, summed over GPUs.
-Prints ONE JSON line on rank 0.
+Next to it, in the same JSON line: the same through the public autograd API with host buffers (`e2e`),
+the dominant kernel's roofline fraction, the CPU baseline, a full 370M training step (`train_370m`) and
+two token-sharded inference runs (`infer_128m`, `prefill_1p3b`).  Prints ONE JSON line on rank 0.
 """
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -29,15 +33,21 @@ import torch  # noqa: E402
 
 WORKLOAD = dict(name="flashmhf_370m_layer_op_fwd_bwd", B=16, S=2048, H=8, Hkuv=8, Dh=128, E=11, De=256)
 NOMINAL_BF16_TFLOPS = 2250.0
-# DRAM bytes (read + write) per launch on this workload, from one `ncu --set full` capture of each kernel
-# (profiles/ncu_full_fwd_bwd_kernels_370m_layer_op.md).  Reported as roofline.traffic; the kernels are
-# tensor-bound, so this only shows that nothing is re-read from HBM (Q, dO, O, dQ once; weights from L2).
-NCU_DRAM_BYTES_PER_LAUNCH = {"fwd_kernel": 136.1e6, "bwd_dq_kernel": 227.3e6, "bwd_dw_kernel": 226.5e6}
-CPU_SAMPLE_TOKENS = 8192   # one batch row of this many tokens per CPU pass (~0.5 s on 16 cores)
+KERNEL_SOURCES = ("tc_common.cuh", "tc_fwd.cu", "tc_bwd.cu")
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "ncu_dram_traffic.json")
+CPU_CHUNK_ROWS = 4          # the CPU legs walk the batch in chunks of this many rows to bound host memory
 
 
 def alg_flops(B, S, H, Dh, E, De, passes=18):
     return passes * B * S * H * E * De * Dh
+
+
+def workload_config(w, world):
+    """What both arms print as `config`: a description of the workload only (no measured values)."""
+    return {"workload": w["name"], "B_per_gpu": w["B"], "S": w["S"], "H": w["H"], "Hkuv": w["Hkuv"], "Dh": w["Dh"],
+            "E": w["E"], "De": w["De"], "flops_per_step": "18*T*H*E*De*Dh (recompute not counted)",
+            "l2": "per-step working set (Q, dO, O, dQ, R, dR ~300 MB) exceeds the 126 MB L2",
+            "parallelism": f"dp{world}" + (" + NCCL all-reduce of dK,dU,dV" if world > 1 else "")}
 
 
 def measured_peaks():
@@ -48,6 +58,38 @@ def measured_peaks():
         return dict(burst=float(d["bf16_tflops"]), sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
                     hbm=float(d["hbm_gbs"]), source="measured")
     return dict(burst=1590.0, sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+def kernel_source_digest():
+    """sha256 over the tensor-core kernel sources: ties a recorded ncu figure to the kernels it was taken from."""
+    h = hashlib.sha256()
+    for name in KERNEL_SOURCES:
+        with open(os.path.join(ROOT, "flashmhf_b200", "csrc", name), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def recorded_traffic(kernel, w):
+    """DRAM bytes (read + write) per launch of `kernel` from the recorded ncu capture, or None (with the reason) when
+    the record was taken from other kernel sources or another workload than the ones running now."""
+    try:
+        with open(TRAFFIC_FILE) as f:
+            rec = json.load(f)
+    except (OSError, ValueError):
+        return None, "no recorded capture"
+    if rec.get("kernel_source_sha256") != kernel_source_digest():
+        return None, "recorded capture is of older kernel sources"
+    if any(rec.get("workload", {}).get(k) != w[k] for k in ("B", "S", "H", "Hkuv", "Dh", "E", "De")):
+        return None, "recorded capture is of another workload"
+    v = rec.get("dram_bytes_per_launch", {}).get(kernel)
+    return (float(v), rec.get("command", "")) if v is not None else (None, "kernel not in the recorded capture")
+
+
+def choose_peak(peaks, timed_seconds):
+    """Burst cuBLAS figure for a timed region shorter than a second (clocks have not settled under the power cap),
+    the sustained one otherwise."""
+    kind = "burst" if timed_seconds < 1.0 else "sustained"
+    return kind, peaks[kind]
 
 
 class ClockSampler:
@@ -99,74 +141,125 @@ class ClockSampler:
                 "power_w": statistics.median(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_baseline(w, reps=20, sample_S=CPU_SAMPLE_TOKENS):
-    """The oracle (PyTorch eager restatement of the reference's CPU path, fp32) forward + autograd backward on
-    all host threads, on a bounded sample of the workload: one batch row of `sample_S` tokens."""
-    from oracle import mhffn_oracle as orc
+# --------------------------------------------------------------------------------------- CPU legs
+def find_reference():
+    """A checkout of the reference project, if this machine has one (the GPU boxes normally do not)."""
+    cands = [os.environ.get("FLASHMHF_REFERENCE", ""), os.path.join(ROOT, "baseline", "_ref")]
+    try:
+        with open(os.path.join(ROOT, "BASELINE.json")) as f:
+            cands.append(json.load(f).get("reference_path", ""))
+    except (OSError, ValueError):
+        pass
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "models", "flashmhf", "modeling_mhffnmoe.py")):
+            return c
+    return None
+
+
+def make_cpu_step(w, rows):
+    """One CPU pass (fp32, all host threads) of forward + autograd backward over `rows` batch rows of the workload,
+    walked in chunks of CPU_CHUNK_ROWS rows.  Uses the UNMODIFIED reference layer's eager branch when a checkout of the
+    reference is on this machine (built with skip_linear so that the layer is the head split, the router and the
+    eager loop, models/flashmhf/modeling_mhffnmoe.py:362-430), else the oracle's restatement of that loop.
+    Returns (step function, kind)."""
     torch.set_num_threads(os.cpu_count() or 1)
-    Q, K, U, V, R, dO = orc.make_op_inputs(1, w["H"], sample_S, w["Dh"], w["E"], w["De"], Hkuv=w["Hkuv"], seed=0)
-    ins = [t.requires_grad_(True) for t in (Q, K, U, V, R)]
-    times = []
-    for i in range(reps + 1):
-        for t in ins:
-            t.grad = None
+    H, Hk, Dh, E, De, S = (w[k] for k in ("H", "Hkuv", "Dh", "E", "De", "S"))
+    chunks = [min(CPU_CHUNK_ROWS, rows - i) for i in range(0, rows, CPU_CHUNK_ROWS)]
+    ref = find_reference()
+    if ref is not None:
+        try:
+            from tests.golden.make_golden import load_reference, seeded_params
+            C_, M = load_reference(ref)
+            cfg = C_.MHFFNMoEConfig(hidden_size=H * Dh, intermediate_size=E * De, num_attention_heads=H,
+                                    mhffnmoe_num_heads=H, mhffnmoe_num_kuv_heads=Hk, mhffnmoe_num_experts=E,
+                                    mhffnmoe_use_flash=False, mhffnmoe_custom_init=True, mhffnmoe_apply_rmsnorm=False,
+                                    mhffnmoe_skip_linear=True, rms_norm_eps=1e-5)
+            layer = M.MHFFNMoEMultiHeadFFNFlash(cfg, use_flash=False)
+            seeded_params(layer, 0)
+            g = torch.Generator().manual_seed(0)
+            xs = [torch.randn(c, S, H * Dh, generator=g, requires_grad=True) for c in chunks]
+            gs = [torch.randn(c, S, H * Dh, generator=g) for c in chunks]
+
+            def step():
+                layer.zero_grad(set_to_none=True)
+                for x, gy in zip(xs, gs):
+                    x.grad = None
+                    layer(x).backward(gy)
+            return step, "reference"
+        except Exception as e:  # an unusable checkout is not an error of the benchmark
+            print(f"bench: reference checkout at {ref} not usable ({type(e).__name__}: {e}); timing the oracle port",
+                  file=sys.stderr)
+    from oracle import mhffn_oracle as orc
+    sets = []
+    for i, c in enumerate(chunks):
+        Q, K, U, V, R, dO = orc.make_op_inputs(c, H, S, Dh, E, De, Hkuv=Hk, seed=i)
+        sets.append(([t.requires_grad_(True) for t in (Q, K, U, V, R)], dO))
+
+    def step():
+        for ins, dO in sets:
+            for t in ins:
+                t.grad = None
+            orc.mhffn_forward(*ins).backward(dO)
+    return step, "port"
+
+
+def cpu_baseline(w, seconds=20.0):
+    """The reference's CPU path for the operator, timed on this box's host cores on a bounded sample: whole passes over
+    the full workload, as many as fit in about `seconds` (at least 2)."""
+    step, kind = make_cpu_step(w, w["B"])
+    step()
+    t0 = time.perf_counter()
+    step()
+    first = time.perf_counter() - t0
+    times = [first]
+    while sum(times) < seconds - first and len(times) < 12:
         t0 = time.perf_counter()
-        orc.mhffn_forward(*ins).backward(dO)
-        if i:
-            times.append(time.perf_counter() - t0)
-    fl = alg_flops(1, sample_S, w["H"], w["Dh"], w["E"], w["De"])
+        step()
+        times.append(time.perf_counter() - t0)
     med = statistics.median(times)
-    return {"value": fl / med / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{reps} passes over 1 x {sample_S} tokens of the workload (H={w['H']}, d_h={w['Dh']}, E={w['E']}, "
-                      f"d_e={w['De']}), fp32 eager forward + autograd backward, median pass",
+    fl = alg_flops(w["B"], w["S"], w["H"], w["Dh"], w["E"], w["De"])
+    what = ("the unmodified reference layer's eager branch" if kind == "reference" else
+            "the oracle's restatement of the reference's eager loop")
+    return {"value": fl / med / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
+            "sample": f"{len(times)} passes (after 1 warm-up) over the full workload ({w['B']} x {w['S']} tokens, in chunks of "
+                      f"{CPU_CHUNK_ROWS} rows), {what}, fp32 forward + autograd backward, median pass",
             "seconds_per_pass": med, "seconds_total": sum(times)}
 
 
 def run_reference(args, rank, world):
-    """The reference's CPU path for this operator (eager MH-FFN forward + autograd backward, fp32, all host
-    threads), restated by the oracle.  Each step is one pass over a bounded sample of the workload: one batch
-    row whose token count is chosen from a probe pass so that warm-up + K steps take about two minutes."""
+    """`--impl reference`: the reference's CPU path for this operator on the box's host cores, all threads, on the GPU
+    arm's workload: each step is one pass over the full per-GPU batch (B=16 x S=2048).  If a probe says warm-up + K
+    steps would not end within about four minutes, a step covers fewer batch rows and the line says how many."""
     if rank != 0:
         return
     w = WORKLOAD
-    from oracle import mhffn_oracle as orc
-    torch.set_num_threads(os.cpu_count() or 1)
-
-    def make(tokens):
-        Q, K, U, V, R, dO = orc.make_op_inputs(1, w["H"], tokens, w["Dh"], w["E"], w["De"], Hkuv=w["Hkuv"], seed=0)
-        ins = [t.requires_grad_(True) for t in (Q, K, U, V, R)]
-
-        def step():
-            for t in ins:
-                t.grad = None
-            orc.mhffn_forward(*ins).backward(dO)
-        return step
-
-    probe = make(1024)
+    probe, _ = make_cpu_step(w, 1)
     probe()
     t0 = time.perf_counter()
     probe()
-    per_token = (time.perf_counter() - t0) / 1024
-    target_s = 120.0
-    sample_S = int(target_s / max(1, args.steps + args.warmup) / per_token)
-    sample_S = max(256, min(CPU_SAMPLE_TOKENS, sample_S // 128 * 128))
-    step = make(sample_S)
+    per_row = time.perf_counter() - t0
+    rows = w["B"]
+    budget = 240.0 / max(1, args.steps + args.warmup)
+    if per_row * rows > budget:
+        rows = max(1, int(budget / per_row))
+    step, kind = make_cpu_step(w, rows)
     for _ in range(args.warmup):
         step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         step()
-    dt = (time.perf_counter() - t0) / args.steps
-    val = alg_flops(1, sample_S, w["H"], w["Dh"], w["E"], w["De"]) / dt / 1e12
-    sample = (f"each step = 1 x {sample_S} tokens of the workload, fp32 PyTorch eager forward + autograd backward "
-              f"(the reference's own CPU path restated; the reference itself is Python and is not shipped to this box)")
+    dt = (time.perf_counter() - t0) / max(1, args.steps)
+    val = alg_flops(rows, w["S"], w["H"], w["Dh"], w["E"], w["De"]) / dt / 1e12
+    what = ("the unmodified reference layer's eager branch (use_flash=False)" if kind == "reference" else
+            "the reference's eager loop restated (the reference itself is Python source that is not on this box)")
+    sample = (f"each step = {rows} of the workload's {w['B']} batch rows x {w['S']} tokens, fp32 PyTorch eager forward + "
+              f"autograd backward, {what}")
     print(json.dumps({
         "impl": "reference", "metric": "flashmhf_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w["name"], **{k: w[k] for k in ("B", "S", "H", "Hkuv", "Dh", "E", "De")},
-                   "sample_tokens": sample_S},
-        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+        "config": workload_config(w, world), "rows_per_step": rows,
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
                          "sample": sample},
         "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -188,6 +281,7 @@ def bind_to_gpu_numa_node(index):
         pass
 
 
+# --------------------------------------------------------------------------------------- LM legs
 def lm_train_370m(args, rank, world, dev, sync_all):
     """The second half of the headline metric: full training steps (forward, backward, gradient all-reduce,
     AdamW) of the 370M decoder LM at batch 16 x 2048 per GPU, bf16, uniform random token ids, data-parallel.
@@ -219,6 +313,7 @@ def lm_train_370m(args, rank, world, dev, sync_all):
     e1.record()
     sync_all()
     kernel_ms = _lib.profile_end(capacity=16 * cfg.num_hidden_layers * args.lm_steps + 16)
+    _lib.device_status()
     ms = dp.max_over_ranks(e0.elapsed_time(e1) / args.lm_steps, dev)
     ours_ms = sum(sum(v) for v in kernel_ms.values()) / args.lm_steps
     flops = lm.train_flops_per_token(cfg, St) * Bt * St
@@ -232,6 +327,60 @@ def lm_train_370m(args, rank, world, dev, sync_all):
             "parallelism": f"dp{world}" + (" + per-layer NCCL all-reduce overlapped with backward" if world > 1 else "")}
 
 
+def lm_inference(name, cfg, rows, seq, what, args, rank, world, dev, sync_all):
+    """Token-sharded inference: the batch rows of one request (`rows` x `seq` uniform random token ids, the same on every
+    N) are split over the ranks with dp.shard_range; weights are replicated; no collective in the data path (attention
+    stays inside a sequence, the FFN has no cross-token dependence).  Each timed step copies this rank's ids from pinned
+    host memory, runs the bf16 forward and reads the arg-max of the last position's logits back.  `what` = "logits"
+    (full forward, logits at every position) or "prefill" (hidden states everywhere, logits of the last position).
+    Reports whole-job tokens/s from the slowest rank's time."""
+    from flashmhf_b200 import _lib, dp, lm
+    a, b = dp.shard_range(rows, rank, world) if rank < min(world, rows) else (0, 0)
+    if world > rows:                                   # more ranks than rows: the first `rows` ranks take one row each
+        a, b = (rank, rank + 1) if rank < rows else (0, 0)
+    model = lm.DecoderLM(cfg).init_weights(seed=0).to(dev).to(torch.bfloat16)
+    ids_all = torch.randint(0, cfg.vocab_size, (rows, seq), generator=torch.Generator().manual_seed(0))
+    ids_host = ids_all[a:b].contiguous().pin_memory() if b > a else None
+    out_host = torch.zeros(max(1, b - a), dtype=torch.int64).pin_memory()
+
+    @torch.no_grad()
+    def step():
+        if ids_host is None:
+            return
+        ids = ids_host.to(dev, non_blocking=True)
+        if what == "logits":
+            last = model(ids)[:, -1]
+        else:
+            last = model.lm_head(model.hidden(ids)[:, -1])
+        out_host.copy_(last.float().argmax(-1), non_blocking=True)
+
+    for _ in range(2):
+        step()
+    sync_all()
+    n = args.infer_steps
+    _lib.profile_begin(16 * cfg.num_hidden_layers * n + 16)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        step()
+    e1.record()
+    sync_all()
+    kernel_ms = _lib.profile_end(capacity=16 * cfg.num_hidden_layers * n + 16)
+    _lib.device_status()
+    mine = e0.elapsed_time(e1) / n
+    ms = dp.max_over_ranks(mine, dev)
+    ours = sum(sum(v) for v in kernel_ms.values()) / n
+    share = dp.max_over_ranks(ours / mine if ids_host is not None and mine > 0 else 0.0, dev)
+    del model
+    torch.cuda.empty_cache()
+    return {"model": name, "pass": "bf16 forward, " + ("logits at every position" if what == "logits" else
+                                                        "prefill: hidden states of all tokens, logits of the last"),
+            "rows": rows, "seq_len": seq, "tokens_per_s": rows * seq / (ms * 1e-3), "ms_per_step": ms, "steps": n, "warmup": 2,
+            "split": f"batch rows over {min(world, rows)} of {world} ranks, no collective in the data path",
+            "ranks_with_work": min(world, rows), "ffn_kernels_share": share,
+            "h2d_bytes_per_step_per_rank": (b - a) * seq * 8, "d2h_bytes_per_step_per_rank": (b - a) * 8}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -240,8 +389,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="B=2 instead of 16 (for profiler captures)")
-    ap.add_argument("--no-lm", action="store_true", help="skip the 370M LM training-step measurement")
+    ap.add_argument("--no-lm", action="store_true", help="skip the LM measurements (370M training step, inference runs)")
     ap.add_argument("--lm-steps", type=int, default=8)
+    ap.add_argument("--infer-steps", type=int, default=5)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -274,11 +424,14 @@ def main():
     R = torch.randn(B, H, S, E, device=dev, generator=g).sigmoid()
     R = R / R.sum(-1, keepdim=True)
     K, U, V = (torch.randn(Hk, E, De, Dh, device=dev, generator=gw).mul(0.02).bfloat16() for _ in range(3))
+    bucket = dp.WeightGradBucket(K)   # dK, dU, dV as three views of one all-reduce buffer
 
     def device_step():
         O = fm.forward_raw(Q, K, U, V, R)
-        dQ, dK, dU, dV, dR = fm.backward_raw(Q, K, U, V, R, dO)
-        dp.allreduce_weight_grads([dK, dU, dV])  # one bucketed NCCL all-reduce; no-op on one GPU
+        # weight gradients first, straight into the bucket; their all-reduce (none on one GPU) runs under the dQ/dR kernel
+        dQ, _, _, _, dR = dp.exchange_under_inputs(
+            lambda views: fm.backward_raw(Q, K, U, V, R, dO, parts="weights", weight_grads=views),
+            lambda: fm.backward_raw(Q, K, U, V, R, dO, parts="inputs"), bucket)
         return O, dQ, dR
 
     def sync_all():
@@ -351,7 +504,7 @@ def main():
         keep[b] = res                                        # device tensors (dropped here) can be reused
         return res
 
-    e2e_steps = max(4, args.steps // 4)
+    e2e_steps = max(20, args.steps // 4) if not args.small else 4
     for n in range(2):
         e2e_step(n)
     sync_all()
@@ -364,6 +517,7 @@ def main():
     s_main.wait_event(out_done[1])
     e1.record(s_main)
     sync_all()
+    _lib.device_status()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
     h2d = sum(t.numel() * t.element_size() for t in (hQ, hdO, hR))
     d2h = sum(t.numel() * t.element_size() for t in outs_host[0])
@@ -373,33 +527,42 @@ def main():
     value = fl / (ms * 1e-3) / 1e12
     e2e_value = fl / (e2e_ms * 1e-3) / 1e12
 
-    train = None
+    train = infer = prefill = None
     if not args.no_lm and not args.small:
+        from flashmhf_b200 import lm
         del res, outs_host, hQ, hdO, hR, keep, dev_in
         torch.cuda.empty_cache()
         train = lm_train_370m(args, rank, world, dev, sync_all)
+        torch.cuda.empty_cache()
+        infer = lm_inference("128M", lm.LMConfig.lm_128m(), 8, 2048, "logits", args, rank, world, dev, sync_all)
+        prefill = lm_inference("1.3B", lm.LMConfig.lm_1p3b(), 4, 8192, "prefill", args, rank, world, dev, sync_all)
 
     if rank == 0:
         peaks = measured_peaks()
         per_kernel = {k: statistics.mean(v) for k, v in kernel_ms.items()}
-        alg = {"fwd_kernel": 6, "bwd_dq_kernel": 6, "bwd_dw_kernel": 6}  # algorithmic GEMM passes (x T*H*I*d_h)
+        alg = {"fwd_kernel": 6, "bwd_dq_kernel": 6, "bwd_dw_kernel": 6}  # algorithmic FLOPs / (T*H*I*d_h): 3 GEMM passes each
         top = max((k for k in per_kernel if k in alg), key=lambda k: per_kernel[k])
         achieved = alg_flops(B, S, H, Dh, E, De, passes=alg[top]) / (per_kernel[top] * 1e-3) / 1e12
-        roof = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peaks["sustained"], "unit": "TFLOP/s",
-                "frac": achieved / peaks["sustained"], "peak_source": peaks["source"] + " cuBLAS bf16, sustained",
-                "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(top) if not args.small else None,
-                "traffic_unit": "bytes of DRAM read+write per launch (one ncu capture)", "kernel_ms": per_kernel,
+        peak_kind, peak = choose_peak(peaks, ms * 1e-3 * args.steps)
+        traffic, traffic_note = recorded_traffic(top, w)
+        roof = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak,
+                "peak_source": f"{peaks['source']} cuBLAS bf16, {peak_kind} (timed region {ms * 1e-3 * args.steps:.2f} s)",
+                "frac_of_burst": achieved / peaks["burst"], "frac_of_sustained": achieved / peaks["sustained"],
+                "traffic": traffic, "traffic_note": traffic_note,
+                "traffic_unit": "bytes of DRAM read+write per launch (one ncu capture of these kernel sources)",
+                "kernel_ms": per_kernel,
+                "kernel_frac_of_burst": {k: alg_flops(B, S, H, Dh, E, De, passes=alg[k]) / (per_kernel[k] * 1e-3) / 1e12 /
+                                         peaks["burst"] for k in per_kernel if k in alg},
                 "whole_step_frac_of_nominal_2250": value / world / NOMINAL_BF16_TFLOPS,
-                "whole_step_frac_of_measured": value / world / peaks["sustained"]}
+                "whole_step_frac_of_burst": value / world / peaks["burst"],
+                "whole_step_frac_of_sustained": value / world / peaks["sustained"]}
         out = {
             "metric": "flashmhf_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": w["name"], "B_per_gpu": B, "S": S, "H": H, "Hkuv": Hk, "Dh": Dh, "E": E, "De": De,
-                       "tokens_per_s": B * S * world / (ms * 1e-3),
-                       "flops_per_step": "18*T*H*E*De*Dh (recompute not counted)",
-                       "l2": "per-step working set (Q, dO, O, dQ, R, dR ~300 MB) exceeds the 126 MB L2",
-                       "parallelism": f"dp{world}" + (" + NCCL all-reduce of dK,dU,dV" if world > 1 else "")},
+            "config": workload_config(w, world),
+            "tokens_per_s": B * S * world / (ms * 1e-3),
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                     "pipeline": "copy-in, kernels and copy-out of consecutive steps overlap (3 streams, 2 buffer sets)"},
@@ -410,6 +573,8 @@ def main():
         if train is not None:
             train["mfu_of_measured_sustained"] = train["model_tflops_per_gpu"] / peaks["sustained"]
             out["train_370m"] = train
+            out["infer_128m"] = infer
+            out["prefill_1p3b"] = prefill
         if not args.no_cpu_baseline and world == 1:
             out["cpu_baseline"] = cpu_baseline(w)
         print(json.dumps(out))

@@ -3,11 +3,11 @@
 import os
 import sys
 
-from .functional import FlashMHFFunction, backward_raw, flash_mhf, forward_raw  # noqa: F401
+from .functional import FlashMHFFunction, backward_raw, check_device_status, flash_mhf, forward_raw  # noqa: F401
 
 from .layer import expert_views, fused_prologue, mhffn_layer  # noqa: F401,E402
 
-__all__ = ["flash_mhf", "FlashMHFFunction", "forward_raw", "backward_raw", "install_reference_seam",
+__all__ = ["flash_mhf", "FlashMHFFunction", "forward_raw", "backward_raw", "check_device_status", "install_reference_seam",
            "fused_prologue", "mhffn_layer", "expert_views"]
 
 

@@ -7,9 +7,11 @@ import threading
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "lib", "libflashmhf_b200.so")
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 BF16, F32_CHECK = 0, 1
+BWD_INPUTS, BWD_WEIGHTS = 1, 2      # flashmhf_bwd_params.parts
+SELFTEST_CODE = 9901                # status code of flashmhf_selftest_bounded_wait
 STATIC_SCRATCH_BYTES = 72 << 20
 
 EXPORTS = ("flashmhf_abi_version", "flashmhf_forward_workspace_bytes", "flashmhf_strerror", "flashmhf_last_cuda_error", "flashmhf_forward",
@@ -17,7 +19,8 @@ EXPORTS = ("flashmhf_abi_version", "flashmhf_forward_workspace_bytes", "flashmhf
            "flashmhf_launch_count", "flashmhf_profile_begin", "flashmhf_profile_end",
            "flashmhf_backward_static_scratch", "flashmhf_prologue_forward",
            "flashmhf_prologue_backward_workspace_bytes", "flashmhf_prologue_backward", "flashmhf_lm_rope",
-           "flashmhf_lm_rmsnorm_forward", "flashmhf_lm_rmsnorm_backward_workspace_bytes", "flashmhf_lm_rmsnorm_backward")
+           "flashmhf_lm_rmsnorm_forward", "flashmhf_lm_rmsnorm_backward_workspace_bytes", "flashmhf_lm_rmsnorm_backward",
+           "flashmhf_selftest_bounded_wait")
 
 
 class Tensor(C.Structure):
@@ -29,15 +32,22 @@ class Dims(C.Structure):
                 ("Hkuv", C.c_int32), ("E", C.c_int32), ("De", C.c_int32), ("dtype", C.c_int32)]
 
 
+class Scaling(C.Structure):
+    _fields_ = [("head_scaling", C.c_float), ("up_scaling", C.c_float), ("final_scaling", C.c_float)]
+
+
+NO_SCALING = (1.0, 1.0, 1.0)
+
+
 class FwdParams(C.Structure):
     _fields_ = [("d", Dims), ("Q", Tensor), ("K", Tensor), ("U", Tensor), ("V", Tensor), ("R", Tensor), ("O", Tensor),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("scale", Scaling)]
 
 
 class BwdParams(C.Structure):
     _fields_ = [("d", Dims), ("Q", Tensor), ("K", Tensor), ("U", Tensor), ("V", Tensor), ("R", Tensor),
                 ("dO", Tensor), ("dQ", Tensor), ("dK", Tensor), ("dU", Tensor), ("dV", Tensor), ("dR", Tensor),
-                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("scale", Scaling), ("parts", C.c_uint32)]
 
 
 class PrologueParams(C.Structure):
@@ -104,6 +114,8 @@ def load():
         lib.flashmhf_lm_rmsnorm_backward.restype = C.c_int
         lib.flashmhf_lm_rmsnorm_backward.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                      C.c_size_t, C.c_int64, C.c_int32, C.c_float, C.c_void_p]
+        lib.flashmhf_selftest_bounded_wait.restype = C.c_int
+        lib.flashmhf_selftest_bounded_wait.argtypes = [C.c_longlong, C.c_void_p]
         lib.flashmhf_device_status.restype = C.c_int
         lib.flashmhf_device_status.argtypes = [C.POINTER(C.c_int)]
         lib.flashmhf_launch_count.restype = C.c_uint64
@@ -126,12 +138,16 @@ def check(status):
 
 
 def device_status():
-    """Synchronise the current device and raise if a kernel gave up on a bounded wait."""
+    """Synchronise the current device and raise if a kernel gave up on a bounded wait since the last call.
+
+    The launch whose wait ran out left its outputs unwritten; later launches ran normally.  Reading clears the word."""
     code = C.c_int(0)
     st = load().flashmhf_device_status(C.byref(code))
     if st != 0:
         lib = load()
-        raise FlashMHFError(st, lib.flashmhf_strerror(st).decode() + f" (kernel/wait code {code.value})")
+        err = FlashMHFError(st, lib.flashmhf_strerror(st).decode() + f" (kernel/wait code {code.value})")
+        err.code = code.value
+        raise err
 
 
 def launch_count():

@@ -13,7 +13,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libflashmhf_b200.so")
-SOURCES = ["api.cu", "simt_check.cu", "tc_fwd.cu", "tc_bwd.cu", "prologue.cu", "lm_aux.cu"]
+SOURCES = ["api.cu", "simt_check.cu", "tc_fwd.cu", "tc_bwd.cu", "prologue.cu", "lm_aux.cu", "selftest.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 

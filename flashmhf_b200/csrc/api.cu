@@ -9,20 +9,23 @@
 
 namespace fmhf {
 
-// One status word per device.  Kernels set it (first failure wins) when a bounded wait runs out.
+// Per device: the status word (first failure wins) and the sequence number of the launch that failed.
 static __device__ int g_status_word;
+static __device__ unsigned g_abort_seq;
 
 namespace {
 std::atomic<uint64_t> g_launches{0};
+std::atomic<unsigned> g_seq{0};
 thread_local char tl_cuda_error[256] = "";
 constexpr int kMaxDevices = 64;
 std::mutex g_mu;
-int *g_status_addr[kMaxDevices] = {nullptr};
+DeviceCtl g_ctl[kMaxDevices];
+std::atomic<bool> g_ctl_ready[kMaxDevices];
 }  // namespace
 
 namespace {
 struct Profile {
-    bool on = false;
+    std::atomic<bool> on{false};
     std::vector<cudaEvent_t> ev;
     std::vector<int> tag;
     size_t n = 0;
@@ -41,21 +44,46 @@ void set_cuda_error(cudaError_t e, const char *where) {
     snprintf(tl_cuda_error, sizeof(tl_cuda_error), "%s: %s", where, cudaGetErrorString(e));
 }
 
-int *device_status_ptr() {
+unsigned next_launch_seq() {
+    unsigned s = ++g_seq;
+    return s ? s : ++g_seq;
+}
+
+const DeviceCtl *device_ctl() {
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
-    std::lock_guard<std::mutex> lk(g_mu);
-    if (!g_status_addr[dev]) {
-        void *p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
-        g_status_addr[dev] = static_cast<int *>(p);
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        set_cuda_error(e, "cudaGetDevice");
+        return nullptr;
     }
-    return g_status_addr[dev];
+    if (g_ctl_ready[dev].load(std::memory_order_acquire)) return &g_ctl[dev];
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_ctl_ready[dev].load(std::memory_order_relaxed)) {
+        void *ps = nullptr, *pa = nullptr;
+        int sms = 0;
+        e = cudaGetSymbolAddress(&ps, g_status_word);
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&pa, g_abort_seq);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess || sms < 1) {
+            set_cuda_error(e, "device set-up (status word, SM count)");
+            return nullptr;
+        }
+        g_ctl[dev].status = static_cast<int *>(ps);
+        g_ctl[dev].abort_seq = static_cast<unsigned *>(pa);
+        g_ctl[dev].num_sms = sms;
+        g_ctl[dev].device = dev;
+        g_ctl_ready[dev].store(true, std::memory_order_release);
+    }
+    return &g_ctl[dev];
 }
 
 namespace {
 
-bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+int check_scaling(const flashmhf_scaling &s) {
+    for (float v : {s.head_scaling, s.up_scaling, s.final_scaling})
+        if (!(v == v) || v == 0.f || v - v != 0.f) return FLASHMHF_ERR_BAD_SHAPE;  // NaN, zero or infinite
+    return FLASHMHF_OK;
+}
 
 int check_dims(const flashmhf_dims &d) {
     if (d.dtype != FLASHMHF_BF16 && d.dtype != FLASHMHF_F32_CHECK) return FLASHMHF_ERR_BAD_DTYPE;
@@ -67,9 +95,11 @@ int check_dims(const flashmhf_dims &d) {
     return FLASHMHF_OK;
 }
 
-int check_tensor(const flashmhf_tensor &t) {
+// `align`: 16 bytes for the bf16 tensors (TMA), 4 for the routing weights and their gradient, which the
+// kernels read and write one fp32 element at a time.
+int check_tensor(const flashmhf_tensor &t, unsigned align = 16) {
     if (!t.ptr) return FLASHMHF_ERR_NULL;
-    if (!aligned16(t.ptr)) return FLASHMHF_ERR_MISALIGNED;
+    if ((reinterpret_cast<uintptr_t>(t.ptr) & (align - 1u)) != 0) return FLASHMHF_ERR_MISALIGNED;
     for (int i = 0; i < 3; ++i)
         if (t.stride[i] < 0) return FLASHMHF_ERR_BAD_STRIDE;
     return FLASHMHF_OK;
@@ -123,11 +153,13 @@ int flashmhf_forward(const flashmhf_fwd_params *p, void *stream) {
     if (!p) return FLASHMHF_ERR_NULL;
     int rc = check_dims(p->d);
     if (rc) return rc;
-    const flashmhf_tensor *ts[] = {&p->Q, &p->K, &p->U, &p->V, &p->R, &p->O};
+    if ((rc = check_scaling(p->scale)) != 0) return rc;
+    const flashmhf_tensor *ts[] = {&p->Q, &p->K, &p->U, &p->V, &p->O};
     for (const flashmhf_tensor *t : ts)
         if ((rc = check_tensor(*t)) != 0) return rc;
+    if ((rc = check_tensor(p->R, 4)) != 0) return rc;
     if ((rc = check_arch()) != 0) return rc;
-    if (!device_status_ptr()) return FLASHMHF_ERR_CUDA;
+    if (!device_ctl()) return FLASHMHF_ERR_CUDA;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int n = 0;
     if (p->d.dtype == FLASHMHF_F32_CHECK) {
@@ -155,45 +187,78 @@ size_t flashmhf_backward_workspace_bytes(const flashmhf_dims *d) {
     return tc_backward_workspace_bytes(*d);
 }
 
-int flashmhf_backward(const flashmhf_bwd_params *p, void *stream) {
+// Shared argument checks of the two backward entry points.  Tensors of a part that is not asked for are not looked at.
+static int check_bwd(const flashmhf_bwd_params *p, unsigned *parts_out) {
     if (!p) return FLASHMHF_ERR_NULL;
     int rc = check_dims(p->d);
     if (rc) return rc;
-    const flashmhf_tensor *ts[] = {&p->Q, &p->K, &p->U, &p->V, &p->R, &p->dO, &p->dQ, &p->dK, &p->dU, &p->dV, &p->dR};
-    for (const flashmhf_tensor *t : ts)
+    if ((rc = check_scaling(p->scale)) != 0) return rc;
+    if (p->parts & ~(FLASHMHF_BWD_INPUTS | FLASHMHF_BWD_WEIGHTS)) return FLASHMHF_ERR_BAD_SHAPE;
+    const unsigned parts = p->parts ? p->parts : (FLASHMHF_BWD_INPUTS | FLASHMHF_BWD_WEIGHTS);
+    for (const flashmhf_tensor *t : {&p->Q, &p->K, &p->U, &p->V, &p->dO})
         if ((rc = check_tensor(*t)) != 0) return rc;
-    const size_t need = flashmhf_backward_workspace_bytes(&p->d);
-    if (need > 0 && (!p->workspace || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255u)))
-        return FLASHMHF_ERR_WORKSPACE;
+    if ((rc = check_tensor(p->R, 4)) != 0) return rc;
+    if (parts & FLASHMHF_BWD_INPUTS) {
+        if ((rc = check_tensor(p->dQ)) != 0) return rc;
+        if ((rc = check_tensor(p->dR, 4)) != 0) return rc;
+    }
+    if (parts & FLASHMHF_BWD_WEIGHTS)
+        for (const flashmhf_tensor *t : {&p->dK, &p->dU, &p->dV})
+            if ((rc = check_tensor(*t)) != 0) return rc;
+    *parts_out = parts;
+    return FLASHMHF_OK;
+}
+
+int flashmhf_backward(const flashmhf_bwd_params *p, void *stream) {
+    unsigned parts = 0;
+    int rc = check_bwd(p, &parts);
+    if (rc) return rc;
+    if (parts & FLASHMHF_BWD_WEIGHTS) {
+        const size_t need = flashmhf_backward_workspace_bytes(&p->d);
+        if (need > 0 && (!p->workspace || p->workspace_bytes < need || (reinterpret_cast<uintptr_t>(p->workspace) & 255u)))
+            return FLASHMHF_ERR_WORKSPACE;
+    }
     if ((rc = check_arch()) != 0) return rc;
-    if (!device_status_ptr()) return FLASHMHF_ERR_CUDA;
+    if (!device_ctl()) return FLASHMHF_ERR_CUDA;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int n = 0;
+    flashmhf_bwd_params q = *p;
+    q.parts = parts;
     if (p->d.dtype == FLASHMHF_F32_CHECK) {
-        cudaError_t e = simt_backward(*p, st, &n);
+        cudaError_t e = simt_backward(q, st, &n);
         if (e != cudaSuccess) {
             set_cuda_error(e, "check backward launch");
             rc = FLASHMHF_ERR_CUDA;
         }
     } else {
-        rc = tc_backward(*p, st, &n);
+        rc = tc_backward(q, st, &n);
     }
     g_launches += (uint64_t)n;
     return rc;
 }
 
 int flashmhf_backward_static_scratch(const flashmhf_bwd_params *p, void *stream) {
-    if (!p) return FLASHMHF_ERR_NULL;
-    int rc = check_dims(p->d);
+    unsigned parts = 0;
+    int rc = check_bwd(p, &parts);
     if (rc) return rc;
     if (p->d.dtype != FLASHMHF_BF16) return FLASHMHF_ERR_BAD_DTYPE;
-    const flashmhf_tensor *ts[] = {&p->Q, &p->K, &p->U, &p->V, &p->R, &p->dO, &p->dQ, &p->dK, &p->dU, &p->dV, &p->dR};
-    for (const flashmhf_tensor *t : ts)
-        if ((rc = check_tensor(*t)) != 0) return rc;
     if ((rc = check_arch()) != 0) return rc;
-    if (!device_status_ptr()) return FLASHMHF_ERR_CUDA;
+    if (!device_ctl()) return FLASHMHF_ERR_CUDA;
     int n = 0;
-    rc = tc_backward_static_scratch(*p, static_cast<cudaStream_t>(stream), &n);
+    flashmhf_bwd_params q = *p;
+    q.parts = parts;
+    rc = tc_backward_static_scratch(q, static_cast<cudaStream_t>(stream), &n);
+    g_launches += (uint64_t)n;
+    return rc;
+}
+
+int flashmhf_selftest_bounded_wait(long long limit_cycles, void *stream) {
+    if (limit_cycles < 1 || limit_cycles > kDefaultWaitLimitCycles) return FLASHMHF_ERR_BAD_SHAPE;
+    int rc = check_arch();
+    if (rc) return rc;
+    if (!device_ctl()) return FLASHMHF_ERR_CUDA;
+    int n = 0;
+    rc = selftest_bounded_wait(limit_cycles, static_cast<cudaStream_t>(stream), &n);
     g_launches += (uint64_t)n;
     return rc;
 }
@@ -306,8 +371,9 @@ int flashmhf_profile_end(float *ms, int *tags, int capacity, int *n_out) {
 
 int flashmhf_device_status(int *code) {
     if (code) *code = 0;
-    int *addr = device_status_ptr();
-    if (!addr) return FLASHMHF_ERR_CUDA;
+    const DeviceCtl *ctl = device_ctl();
+    if (!ctl) return FLASHMHF_ERR_CUDA;
+    int *addr = ctl->status;
     cudaError_t e = cudaDeviceSynchronize();
     int v = 0;
     if (e == cudaSuccess) e = cudaMemcpy(&v, addr, sizeof(int), cudaMemcpyDeviceToHost);

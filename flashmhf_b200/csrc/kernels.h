@@ -7,8 +7,35 @@
 
 namespace fmhf {
 
-// Device status word: 0, or the code of the first bounded wait that ran out.
-int *device_status_ptr();  // device address of the per-device status word (resolved once per device)
+// Per-device control words and facts, resolved once per device (with that device current).
+//   status    : 0, or the code of the first bounded wait that ran out since the host last read it
+//   abort_seq : sequence number of the launch whose wait ran out; the other CTAs of THAT launch see it at
+//               their start and return at once, later launches (other numbers) run normally
+struct DeviceCtl {
+    int *status = nullptr;
+    unsigned *abort_seq = nullptr;
+    int num_sms = 0;
+    int device = -1;
+};
+const DeviceCtl *device_ctl();  // nullptr if the device query failed
+unsigned next_launch_seq();     // process-wide, never 0
+// SM count of the current device (the B200's 148 when no device can be queried, e.g. sizing a workspace on a CPU-only host).
+inline int num_sms() {
+    const DeviceCtl *c = device_ctl();
+    return c ? c->num_sms : 148;
+}
+
+// What every tensor-core kernel needs for its bounded waits.
+struct WaitArgs {
+    int *status;
+    unsigned *abort_seq;
+    unsigned seq;
+    long long limit_cycles;
+};
+constexpr long long kDefaultWaitLimitCycles = 3LL << 30;  // ~1.5 s at 1.4-1.9 GHz; a healthy kernel waits microseconds
+inline WaitArgs wait_args(const DeviceCtl *c) {
+    return WaitArgs{c->status, c->abort_seq, next_launch_seq(), kDefaultWaitLimitCycles};
+}
 
 // ---- fp32 check kernels (CUDA cores) -------------------------------------------------------
 cudaError_t simt_forward(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch);
@@ -36,6 +63,7 @@ int lm_rmsnorm_backward(const void *x, const float *w, const void *g, void *dx, 
                         size_t workspace_bytes, long long rows, int n, float eps, cudaStream_t st, int *n_launch);
 
 void set_cuda_error(cudaError_t e, const char *where);
+int selftest_bounded_wait(long long limit_cycles, cudaStream_t st, int *n_launch);
 
 // Kernel-boundary marks for the profiling aid (flashmhf_profile_begin/end): records an event on
 // `st` tagged `tag` when profiling is on, does nothing otherwise.

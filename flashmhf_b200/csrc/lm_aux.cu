@@ -10,7 +10,6 @@ namespace fmhf {
 namespace {
 
 constexpr int kWarpsAux = 8;
-constexpr int kNumSMsAux = 148;
 
 __device__ __forceinline__ float warp_sum32(float v) {
 #pragma unroll
@@ -157,7 +156,7 @@ __global__ void __launch_bounds__(128) aux_reduce_kernel(const float *part, floa
 }
 
 int norm_blocks(long long rows) {
-    const long long most = (rows + kWarpsAux - 1) / kWarpsAux, want = 2 * kNumSMsAux;
+    const long long most = (rows + kWarpsAux - 1) / kWarpsAux, want = 2 * num_sms();
     return (int)(want < most ? want : most);
 }
 bool norm_ok(long long rows, int n) { return rows >= 1 && (n == 768 || n == 1024 || n == 2048); }
@@ -174,7 +173,8 @@ int lm_rope(const void *x, void *y, const float *cos_t, const float *sin_t, long
         return FLASHMHF_ERR_BAD_STRIDE;
     const long long items = tokens * heads * (hd / 16);
     const long long blocks = (items + 255) / 256;
-    const int grid = (int)(blocks < 8LL * kNumSMsAux ? blocks : 8LL * kNumSMsAux);
+    const long long cap = 8LL * num_sms();
+    const int grid = (int)(blocks < cap ? blocks : cap);
     rope_kernel<<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), static_cast<__nv_bfloat16 *>(y), cos_t, sin_t,
                                      items, S, heads, hd, x_tok, y_tok, transpose ? -1.f : 1.f);
     *n_launch += 1;

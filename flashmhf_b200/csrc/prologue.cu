@@ -31,7 +31,6 @@ namespace {
 constexpr int kWarps = 8;             // warps per block
 constexpr int kNR = 2;                // rows a warp has in flight
 constexpr int kMaxE = 32;
-constexpr int kNumSMs = 148;
 constexpr int kFwdBlocksPerSM = 2;
 
 // Row pair q of warp `warp` in block column `by` of `gy`: pairs are dealt round-robin over warps, then blocks.
@@ -389,7 +388,8 @@ bool use_mma(const flashmhf_prologue_params &p) { return p.E <= 24; }
 int blocks_per_head(const flashmhf_prologue_params &p, int per_sm) {
     const int unit = use_mma(p) ? 16 : kNR;
     const long long pairs = ((long long)p.B * p.S + unit - 1) / unit, most = (pairs + kWarps - 1) / kWarps;
-    const long long want = kNumSMs * per_sm / p.H > 1 ? kNumSMs * per_sm / p.H : 1;
+    const int sms = num_sms();
+    const long long want = sms * per_sm / p.H > 1 ? sms * per_sm / p.H : 1;
     return (int)(want < most ? want : most);
 }
 

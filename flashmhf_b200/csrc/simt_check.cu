@@ -22,6 +22,7 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 struct Dims {
     int B, H, S, Dh, Hkuv, E, De, G;
+    float s0, s1, s2;  // head, up and final scaling:  M = s0 Q K^T,  N = s1 Q U^T,  A = silu(M) N r s2
 };
 
 struct T4 {
@@ -59,10 +60,10 @@ __global__ void __launch_bounds__(256) simt_fwd_kernel(Dims d, T4 Q, T4 K, T4 U,
                 n += qv[i] * (ok ? u[c] : 0.f);
                 vv[i] = ok ? v[c] : 0.f;
             }
-            m = warp_sum(m);
-            n = warp_sum(n);
+            m = warp_sum(m) * d.s0;
+            n = warp_sum(n) * d.s1;
             const float sg = 1.f / (1.f + expf(-m));
-            const float a = m * sg * n * re;
+            const float a = m * sg * n * re * d.s2;
 #pragma unroll
             for (int i = 0; i < kMaxNQ; ++i) acc[i] += a * vv[i];
         }
@@ -111,14 +112,14 @@ __global__ void __launch_bounds__(256) simt_bwd_dq_kernel(Dims d, T4 Q, T4 K, T4
                 n += qv[i] * uv[i];
                 da += gv[i] * (ok ? v[c] : 0.f);
             }
-            m = warp_sum(m);
-            n = warp_sum(n);
-            da = warp_sum(da);
+            m = warp_sum(m) * d.s0;
+            n = warp_sum(n) * d.s1;
+            da = warp_sum(da) * d.s2;   // gradient w.r.t. the unscaled product silu(M) N r
             const float sg = 1.f / (1.f + expf(-m));
             const float s = m * sg;
             dre += da * s * n;
-            const float dm = da * (re * n) * (sg + s * (1.f - sg));
-            const float dn = da * s * re;
+            const float dm = da * (re * n) * (sg + s * (1.f - sg)) * d.s0;  // w.r.t. Q K^T
+            const float dn = da * s * re * d.s1;                            // w.r.t. Q U^T
 #pragma unroll
             for (int i = 0; i < kMaxNQ; ++i) acc[i] += dm * kv[i] + dn * uv[i];
         }
@@ -170,14 +171,14 @@ __global__ void __launch_bounds__(256) simt_bwd_dw_kernel(Dims d, T4 Q, T4 K, T4
                     n += qv[i] * uv[i];
                     da += gv[i] * vv[i];
                 }
-                m = warp_sum(m);
-                n = warp_sum(n);
-                da = warp_sum(da);
+                m = warp_sum(m) * d.s0;
+                n = warp_sum(n) * d.s1;
+                da = warp_sum(da) * d.s2;
                 const float sg = 1.f / (1.f + expf(-m));
                 const float s = m * sg;
-                const float a = s * n * re;
-                const float dm = da * (re * n) * (sg + s * (1.f - sg));
-                const float dn = da * s * re;
+                const float a = s * n * re * d.s2;
+                const float dm = da * (re * n) * (sg + s * (1.f - sg)) * d.s0;
+                const float dn = da * s * re * d.s1;
 #pragma unroll
                 for (int i = 0; i < kMaxNQ; ++i) {
                     ak[i] += dm * qv[i];
@@ -201,14 +202,16 @@ __global__ void __launch_bounds__(256) simt_bwd_dw_kernel(Dims d, T4 Q, T4 K, T4
 }
 
 T4 t4(const flashmhf_tensor &t) { return T4{static_cast<const float *>(t.ptr), t.stride[0], t.stride[1], t.stride[2]}; }
-Dims dims(const flashmhf_dims &d) { return Dims{d.B, d.H, d.S, d.Dh, d.Hkuv, d.E, d.De, d.H / d.Hkuv}; }
+Dims dims(const flashmhf_dims &d, const flashmhf_scaling &s) {
+    return Dims{d.B, d.H, d.S, d.Dh, d.Hkuv, d.E, d.De, d.H / d.Hkuv, s.head_scaling, s.up_scaling, s.final_scaling};
+}
 
 }  // namespace
 
 cudaError_t simt_forward(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
     const long long rows = (long long)p.d.B * p.d.H * p.d.S;
     const unsigned blocks = (unsigned)((rows + 7) / 8);
-    simt_fwd_kernel<<<blocks, 256, 0, st>>>(dims(p.d), t4(p.Q), t4(p.K), t4(p.U), t4(p.V), t4(p.R),
+    simt_fwd_kernel<<<blocks, 256, 0, st>>>(dims(p.d, p.scale), t4(p.Q), t4(p.K), t4(p.U), t4(p.V), t4(p.R),
                                             static_cast<float *>(p.O.ptr), p.O.stride[0], p.O.stride[1], p.O.stride[2]);
     *n_launch += 1;
     return cudaGetLastError();
@@ -216,18 +219,24 @@ cudaError_t simt_forward(const flashmhf_fwd_params &p, cudaStream_t st, int *n_l
 
 cudaError_t simt_backward(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch) {
     const long long rows = (long long)p.d.B * p.d.H * p.d.S;
-    simt_bwd_dq_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
-        dims(p.d), t4(p.Q), t4(p.K), t4(p.U), t4(p.V), t4(p.R), t4(p.dO), static_cast<float *>(p.dQ.ptr),
-        p.dQ.stride[0], p.dQ.stride[1], p.dQ.stride[2], static_cast<float *>(p.dR.ptr), p.dR.stride[0],
-        p.dR.stride[1], p.dR.stride[2]);
-    *n_launch += 1;
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
-    const long long wrows = (long long)p.d.Hkuv * p.d.E * p.d.De;
-    simt_bwd_dw_kernel<<<(unsigned)((wrows + 7) / 8), 256, 0, st>>>(dims(p.d), t4(p.Q), t4(p.K), t4(p.U), t4(p.V),
-                                                                   t4(p.R), t4(p.dO), t4(p.dK), t4(p.dU), t4(p.dV));
-    *n_launch += 1;
-    return cudaGetLastError();
+    cudaError_t e = cudaSuccess;
+    if (p.parts & FLASHMHF_BWD_INPUTS) {
+        simt_bwd_dq_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(
+            dims(p.d, p.scale), t4(p.Q), t4(p.K), t4(p.U), t4(p.V), t4(p.R), t4(p.dO), static_cast<float *>(p.dQ.ptr),
+            p.dQ.stride[0], p.dQ.stride[1], p.dQ.stride[2], static_cast<float *>(p.dR.ptr), p.dR.stride[0],
+            p.dR.stride[1], p.dR.stride[2]);
+        *n_launch += 1;
+        if ((e = cudaGetLastError()) != cudaSuccess) return e;
+    }
+    if (p.parts & FLASHMHF_BWD_WEIGHTS) {
+        const long long wrows = (long long)p.d.Hkuv * p.d.E * p.d.De;
+        simt_bwd_dw_kernel<<<(unsigned)((wrows + 7) / 8), 256, 0, st>>>(dims(p.d, p.scale), t4(p.Q), t4(p.K), t4(p.U),
+                                                                       t4(p.V), t4(p.R), t4(p.dO), t4(p.dK), t4(p.dU),
+                                                                       t4(p.dV));
+        *n_launch += 1;
+        e = cudaGetLastError();
+    }
+    return e;
 }
 
 }  // namespace fmhf

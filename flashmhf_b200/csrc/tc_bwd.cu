@@ -23,26 +23,12 @@
 //
 // Both use 384 threads: warp 0 TMA producer, warps 1 and 3 MMA issuers (one per MMA chain; warp 1 owns
 // tensor memory), warps 4-11 element-wise math (warp % 4 = TMEM lane quarter, (warp-4)/4 = which 32 of the 64 block columns).
+#include <atomic>
 #include <mutex>
 
 #include "kernels.h"
 #include "tc_common.cuh"
 #include "tensormap.cuh"
-
-#ifdef FMHF_TRACE
-// Debug build only: per-tile clock stamps of one dK/dU/dV CTA for pipeline analysis.
-__device__ unsigned int g_dw_trace[4][64][8];
-#define FMHF_TRW(role, i, ev)                                                                  \
-    do {                                                                                       \
-        if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0 && (i) < 64)                  \
-            g_dw_trace[role][i][ev] = (unsigned int)clock64();                                  \
-    } while (0)
-extern "C" int flashmhf_debug_read_dw_trace(unsigned int *out) {
-    return (int)cudaMemcpyFromSymbol(out, g_dw_trace, sizeof(g_dw_trace));
-}
-#else
-#define FMHF_TRW(role, i, ev) do { } while (0)
-#endif
 
 namespace fmhf {
 namespace {
@@ -51,19 +37,27 @@ constexpr int kBT = 128, kBI = 64, kThreads = 384, kActThreads = 256;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTile = kBT * 128;    // one 128-row x 64-col SW128 chunk: 16 KB
 constexpr uint32_t kWChunk = kBI * 128;  // one 64-row x 64-col chunk: 8 KB
-constexpr int kNumSMs = 148;
 
 // Element-wise backward math for two neighbouring intermediate columns of one token row, on packed
-// fp32 pairs.  With t = tanh(m/2): sg = sigmoid(m) = 0.5 + 0.5 t, 1 - sg = 0.5 - 0.5 t, s = m*sg,
-// silu'(m) = sg + s*(1 - sg).
-struct BwdPair {
-    f32x2 dm, dn, sn, da;  // dM, dN, s*N (times r gives A, times dA sums to dR), dA
+// fp32 pairs.  m, n are the raw products Q K^T, Q U^T; with the layer's constants s0 (head), s1 (up),
+// s2 (final) the forward is A = silu(s0 m) (s1 n) s2 r.  With t = tanh(s0 m / 2): sg = sigmoid(s0 m) =
+// 0.5 + 0.5 t, s = m*sg (so silu(s0 m) = s0 s), silu'(s0 m) = sg + s * s0 (1 - sg).  All three constants
+// fold into the per-row factor r2 = s0 s1 s2 r and into the two constants below, at no cost per element:
+//   dM = dA r2 n silu'(s0 m),  dN = dA r2 s,  A = s n r2,  dR = s0 s1 s2 * sum dA s n.
+struct BwdConst {
+    f32x2 half_s0, p_half_s0, n_half_s0;  // (s0/2), (s0/2), (-s0/2): tanh argument scale and s0 (1 - sg) = s0/2 - (s0/2) t
 };
-__device__ __forceinline__ BwdPair bwd_pair(f32x2 m, f32x2 n, f32x2 da, f32x2 r2) {
-    const f32x2 half = f2_pack(0.5f, 0.5f), nhalf = f2_pack(-0.5f, -0.5f);
-    const f32x2 t = f2_tanh(f2_mul(m, half));
+__device__ __forceinline__ BwdConst bwd_const(float s0) {
+    return BwdConst{f2_pack(0.5f * s0, 0.5f * s0), f2_pack(0.5f * s0, 0.5f * s0), f2_pack(-0.5f * s0, -0.5f * s0)};
+}
+struct BwdPair {
+    f32x2 dm, dn, sn, da;  // dM, dN, s*N (times r2 gives A, times dA sums to dR / (s0 s1 s2)), dA
+};
+__device__ __forceinline__ BwdPair bwd_pair(f32x2 m, f32x2 n, f32x2 da, f32x2 r2, const BwdConst &k) {
+    const f32x2 half = f2_pack(0.5f, 0.5f);
+    const f32x2 t = f2_tanh(f2_mul(m, k.half_s0));
     const f32x2 sg = f2_fma(t, half, half);
-    const f32x2 omsg = f2_fma(t, nhalf, half);
+    const f32x2 omsg = f2_fma(t, k.n_half_s0, k.p_half_s0);
     const f32x2 s = f2_mul(m, sg);
     const f32x2 dsilu = f2_fma(s, omsg, sg);
     const f32x2 dar = f2_mul(da, r2);
@@ -97,7 +91,7 @@ struct DqSmem {
 };
 
 enum { DQ_QFULL = 0, DQ_KUFULL = 1, DQ_KUEMPTY = 4, DQ_VFULL = 7, DQ_VEMPTY = 9, DQ_SFULL = 11, DQ_SEMPTY = 13,
-       DQ_PFULL = 15, DQ_ACCFULL = 17, DQ_DRFULL = 18, DQ_DAFREE = 20, DQ_BARS = 22 };
+       DQ_PFULL = 15, DQ_ACCFULL = 17, DQ_DRFULL = 18, DQ_DAFREE = 20, DQ_DRFREE = 22, DQ_BARS = 24 };
 
 struct DqArgs {
     const float *R;
@@ -105,7 +99,8 @@ struct DqArgs {
     float *dR;
     long long dr_sb, dr_sh, dr_ss;
     int S, E, De, G;
-    int *status;
+    float s0, c;  // head_scaling; head_scaling * up_scaling * final_scaling
+    WaitArgs wait;
 };
 
 template <int DH>
@@ -128,21 +123,22 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = blockIdx.x * kBT, h = blockIdx.y, b = blockIdx.z, hk = h / args.G;
     const int bpe = args.De / kBI, nblk = args.E * bpe;
-    const WaitCtl ctl{abort_flag, args.status};
+    const WaitCtl ctl{abort_flag, args.wait};
     constexpr int W = kKernelBwdDq * 100;
     constexpr uint32_t kColAcc = 0, kColS0 = 128, kBufStride = 192, kColdA = 128;  // dA offset inside a buffer
 
     if (threadIdx.x == 0) {
-        *abort_flag = (*reinterpret_cast<volatile int *>(args.status) != 0);  // an earlier CTA gave up: drain fast
+        *abort_flag = launch_aborted(args.wait);  // a CTA of this launch gave up: drain fast
         mbar_init(bar(DQ_QFULL), 1);
         for (int s = 0; s < L::kKUStages; ++s) { mbar_init(bar(DQ_KUFULL + s), 1); mbar_init(bar(DQ_KUEMPTY + s), 1); }
         for (int s = 0; s < L::kVStages; ++s) { mbar_init(bar(DQ_VFULL + s), 1); mbar_init(bar(DQ_VEMPTY + s), 1); }
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar(DQ_SFULL + i), 2);             // one commit from each of the two recompute issuers
-            mbar_init(bar(DQ_SEMPTY + i), kActThreads);  // S and dA of the buffer are in registers
-            mbar_init(bar(DQ_PFULL + i), kActThreads);   // [dM|dN] written over the dA columns
+            mbar_init(bar(DQ_SEMPTY + i), arrivals_of(kActThreads));  // S and dA of the buffer are in registers
+            mbar_init(bar(DQ_PFULL + i), arrivals_of(kActThreads));   // [dM|dN] written over the dA columns
             mbar_init(bar(DQ_DAFREE + i), 1);            // the dQ update that read [dM|dN] is done
-            mbar_init(bar(DQ_DRFULL + i), kActThreads / 2);
+            mbar_init(bar(DQ_DRFULL + i), arrivals_of(kActThreads / 2));  // the upper column half has written its dR_e partial
+            mbar_init(bar(DQ_DRFREE + i), arrivals_of(kActThreads / 2));  // the lower half has read it: the row may be reused
         }
         mbar_init(bar(DQ_ACCFULL), 1);
         fence_mbar_init();
@@ -284,6 +280,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
         float r_cur = 0.f, r_next = in_range ? __ldg(rrow) : 0.f;
         f32x2 dr2 = f2_pack(0.f, 0.f);  // running dR_e of this thread's columns (two interleaved partial sums)
+        const BwdConst kc = bwd_const(args.s0);
         bool ok = true;
         int in_e = 0, e = 0;  // block index inside the current sub-network; current sub-network
         for (int j = 0; j < nblk; ++j) {
@@ -297,19 +294,19 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             tc_fence_after();
             const uint32_t tS = lane_base + kColS0 + bb * kBufStride + half * 32;
             uint32_t pm[16], pn[16];  // packed bf16 pairs of dM, dN for this thread's 32 columns
-            const f32x2 r2 = f2_pack(r_cur, r_cur);
+            const f32x2 r2 = f2_pack(args.c * r_cur, args.c * r_cur);
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
                 uint32_t m[16], n[16], da[16];
                 tmem_ld16x3_sync(tS + sub * 16, tS + kBI + sub * 16, tS + kColdA + sub * 16, m, n, da);
                 if (sub == 1) {   // S is in registers: it may be recomputed for block j+2 from here on
                     tc_fence_before();
-                    mbar_arrive(bar(DQ_SEMPTY + bb));
+                    warp_arrive(bar(DQ_SEMPTY + bb));
                 }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const BwdPair x = bwd_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]), f2_pack_bits(n[2 * i], n[2 * i + 1]),
-                                               f2_pack_bits(da[2 * i], da[2 * i + 1]), r2);
+                                               f2_pack_bits(da[2 * i], da[2 * i + 1]), r2, kc);
                     dr2 = f2_fma(x.da, x.sn, dr2);
                     pm[sub * 8 + i] = f2_to_bf16x2(x.dm);
                     pn[sub * 8 + i] = f2_to_bf16x2(x.dn);
@@ -321,18 +318,22 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             tmem_st16(tS + kColdA + 16, pn);
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(bar(DQ_PFULL + bb));
+            warp_arrive(bar(DQ_PFULL + bb));
             if (++in_e == bpe) {  // sub-network finished: add the two column halves of dR_e
                 const int xb = e & 1;
                 float dr_lo, dr_hi;
                 f2_unpack(dr2, dr_lo, dr_hi);
-                const float dr_acc = dr_lo + dr_hi;
+                const float dr_acc = (dr_lo + dr_hi) * args.c;
                 if (half == 1) {
+                    // the exchange row of sub-network e was last used by e - 2: wait until that value has been read
+                    if (e >= 2 && !mbar_wait(bar(DQ_DRFREE + xb), ((e >> 1) - 1) & 1, ctl, W + 11)) { ok = false; break; }
                     drx[xb * 128 + row] = dr_acc;
-                    mbar_arrive(bar(DQ_DRFULL + xb));
+                    warp_arrive(bar(DQ_DRFULL + xb));
                 } else {
                     if (!mbar_wait(bar(DQ_DRFULL + xb), (e >> 1) & 1, ctl, W + 9)) { ok = false; break; }
-                    if (in_range) drrow[e] = dr_acc + drx[xb * 128 + row];
+                    const float other = drx[xb * 128 + row];
+                    warp_arrive(bar(DQ_DRFREE + xb));
+                    if (in_range) drrow[e] = dr_acc + other;
                 }
                 in_e = 0;
                 ++e;
@@ -413,7 +414,8 @@ struct DwArgs {
     float *ws;  // [nsplit][3][Hkuv][I][DH] fp32 partial sums
     int S, E, De, G, B, Hkuv;
     int tiles_per_seq, tiles_total, tiles_per_split;
-    int *status;
+    float s0, c;  // head_scaling; head_scaling * up_scaling * final_scaling
+    WaitArgs wait;
 };
 
 template <int DH>
@@ -438,7 +440,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int tile_begin = split * args.tiles_per_split;
     const int tile_end = min(tile_begin + args.tiles_per_split, args.tiles_total);
     const int ntiles = tile_end - tile_begin;  // >= 1 by construction of the grid
-    const WaitCtl ctl{abort_flag, args.status};
+    const WaitCtl ctl{abort_flag, args.wait};
     constexpr int W = kKernelBwdDw * 100;
     // dV^T = sum_t dO^T A (d_h x 64, M = 128, N = 64) needs half the columns and three quarters of the tensor-pipe
     // time of dV = sum_t A^T dO (M = 64 runs at the M = 128 rate); it needs M = d_h = 128.
@@ -457,7 +459,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     };
 
     if (threadIdx.x == 0) {
-        *abort_flag = (*reinterpret_cast<volatile int *>(args.status) != 0);  // an earlier CTA gave up: drain fast
+        *abort_flag = launch_aborted(args.wait);  // a CTA of this launch gave up: drain fast
         mbar_init(bar(DW_WFULL), 1);
         for (int s = 0; s < L::kTokStages; ++s) {
             mbar_init(bar(DW_QFULL + s), 1);
@@ -467,11 +469,11 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar(DW_SFULL + b), 1);
-            mbar_init(bar(DW_SEMPTY + b), kActThreads);
+            mbar_init(bar(DW_SEMPTY + b), arrivals_of(kActThreads));
         }
-        mbar_init(bar(DW_DAEMPTY), kActThreads);
-        mbar_init(bar(DW_PFULL), kActThreads);
-        mbar_init(bar(DW_AFULL), kActThreads);
+        mbar_init(bar(DW_DAEMPTY), arrivals_of(kActThreads));
+        mbar_init(bar(DW_PFULL), arrivals_of(kActThreads));
+        mbar_init(bar(DW_AFULL), arrivals_of(kActThreads));
         mbar_init(bar(DW_PEMPTY), 1);
         mbar_init(bar(DW_AEMPTY), 1);
         mbar_init(bar(DW_ACCFULL), 1);
@@ -502,10 +504,8 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             for (int i = 0; i < ntiles; ++i) {
                 int ts, hh, bb;
                 tile_coords(i, ts, hh, bb);
-                FMHF_TRW(0, i, 0);
                 const uint32_t d = sTok + st * L::kTokStage;
                 if (!mbar_wait(bar(DW_QEMPTY + st), ph, ctl, W + 1)) break;
-                FMHF_TRW(0, i, 1);
                 const uint32_t fq = bar(DW_QFULL + st);
                 mbar_arrive_expect_tx(fq, L::kTokStage / 2);
 #pragma unroll
@@ -534,13 +534,10 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             int st = 0;
             uint32_t ph = 0;
             for (int i = 0; ok && i < ntiles; ++i) {
-                FMHF_TRW(1, i, 0);
                 if (!mbar_wait(bar(DW_QFULL + st), ph, ctl, W + 4)) break;
-                FMHF_TRW(1, i, 1);
                 const int sb = i % kSB;
                 const uint32_t sph = (uint32_t)(i / kSB) & 1u;
                 if (!mbar_wait(bar(DW_SEMPTY + sb), sph ^ 1, ctl, W + 5)) break;
-                FMHF_TRW(1, i, 2);
                 tc_fence_after();
                 const uint64_t dq = dQk0 + st * kTokStep, dg = dGk0 + st * kTokStep;
 #pragma unroll
@@ -559,7 +556,6 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                             k > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(DW_SFULL + sb));
-                FMHF_TRW(1, i, 3);
                 if (++st == L::kTokStages) { st = 0; ph ^= 1; }
             }
         }
@@ -574,9 +570,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             int st = 0;
             bool ok = true;
             for (int i = 0; i < ntiles; ++i) {
-                FMHF_TRW(1, i, 4);
                 if (!mbar_wait(bar(DW_PFULL), i & 1, ctl, W + 6)) { ok = false; break; }
-                FMHF_TRW(1, i, 5);
                 tc_fence_after();
                 const uint64_t dq = dQmn0 + st * kTokStep, dg = dGmn0 + st * kTokStep;
 #pragma unroll
@@ -593,7 +587,6 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 }
                 umma_commit(bar(DW_GEMPTY + st));  // dO of this stage and the A tile are free
                 umma_commit(bar(DW_AEMPTY));
-                FMHF_TRW(1, i, 6);
                 if (++st == L::kTokStages) st = 0;
             }
             if (ok) umma_commit(bar(DW_ACCFULL));
@@ -603,6 +596,7 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const int row = quarter * 32 + lane;
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
         bool ok = true;
+        const BwdConst kc = bwd_const(args.s0);
         float r_next;
         {
             int ts, hh, bb;
@@ -620,16 +614,14 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 r_next = (t < args.S) ? __ldg(args.R + (long long)bb * args.r_sb + (long long)hh * args.r_sh +
                                               (long long)t * args.r_ss + e) : 0.f;
             }
-            FMHF_TRW(2 + half, i, 0);
             const int sb = i % kSB;
             if (!mbar_wait(bar(DW_SFULL + sb), (uint32_t)(i / kSB) & 1u, ctl, W + 7)) { ok = false; break; }
-            FMHF_TRW(2 + half, i, 1);
             tc_fence_after();
             uint32_t pm[16], pn[16], pa[16], da[32];
             tmem_ld32_sync(lane_base + kColdA + half * 32, da);   // dA first: its single buffer goes straight back
             tc_fence_before();
-            mbar_arrive(bar(DW_DAEMPTY));
-            const f32x2 r2 = f2_pack(r, r);
+            warp_arrive(bar(DW_DAEMPTY));
+            const f32x2 r2 = f2_pack(args.c * r, args.c * r);
             const uint32_t colS = kColS + sb * 2 * kBI;
 #pragma unroll
             for (int sub = 0; sub < 2; ++sub) {
@@ -638,20 +630,18 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 tmem_ld16x2_sync(lane_base + colS + c, lane_base + colS + kBI + c, m, n);
                 if (sub == 1) {   // S is in registers: the buffer can take the tile after next
                     tc_fence_before();
-                    mbar_arrive(bar(DW_SEMPTY + sb));
+                    warp_arrive(bar(DW_SEMPTY + sb));
                 }
 #pragma unroll
                 for (int q = 0; q < 8; ++q) {
                     const BwdPair x = bwd_pair(f2_pack_bits(m[2 * q], m[2 * q + 1]), f2_pack_bits(n[2 * q], n[2 * q + 1]),
-                                               f2_pack_bits(da[sub * 16 + 2 * q], da[sub * 16 + 2 * q + 1]), r2);
+                                               f2_pack_bits(da[sub * 16 + 2 * q], da[sub * 16 + 2 * q + 1]), r2, kc);
                     pm[sub * 8 + q] = f2_to_bf16x2(x.dm);
                     pn[sub * 8 + q] = f2_to_bf16x2(x.dn);
                     pa[sub * 8 + q] = f2_to_bf16x2(f2_mul(x.sn, r2));
                 }
             }
-            FMHF_TRW(2 + half, i, 2);
             if (!mbar_wait(bar(DW_PEMPTY), (i & 1) ^ 1, ctl, W + 8)) { ok = false; break; }
-            FMHF_TRW(2 + half, i, 3);
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const uint32_t off = sw128_offset(row, half * 4 + q);
@@ -659,14 +649,13 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 st_shared_v4(sP + kTile + off, pn[4 * q], pn[4 * q + 1], pn[4 * q + 2], pn[4 * q + 3]);
             }
             fence_async_smem();
-            mbar_arrive(bar(DW_PFULL));
+            warp_arrive(bar(DW_PFULL));
             if (!mbar_wait(bar(DW_AEMPTY), (i & 1) ^ 1, ctl, W + 8)) { ok = false; break; }
 #pragma unroll
             for (int q = 0; q < 4; ++q)
                 st_shared_v4(sA + sw128_offset(row, half * 4 + q), pa[4 * q], pa[4 * q + 1], pa[4 * q + 2], pa[4 * q + 3]);
             fence_async_smem();
-            mbar_arrive(bar(DW_AFULL));
-            FMHF_TRW(2 + half, i, 4);
+            warp_arrive(bar(DW_AFULL));
         }
         if (ok) ok = mbar_wait(bar(DW_ACCFULL), 0, ctl, W + 9);
         if (ok) {
@@ -760,13 +749,13 @@ __global__ void __launch_bounds__(256) dw_reduce_kernel(const ReduceArgs a) {
     }
 }
 
-int choose_nsplit(long long items, int tiles_total) {
+int choose_nsplit(long long items, int tiles_total, int num_sms) {
     int best = 1;
     double best_eff = 0.0;
     for (int ns = 1; ns <= 16 && ns <= tiles_total; ++ns) {
         const long long ctas = items * ns;
-        const long long waves = (ctas + kNumSMs - 1) / kNumSMs;
-        const double eff = (double)ctas / (double)(waves * kNumSMs);
+        const long long waves = (ctas + num_sms - 1) / num_sms;
+        const double eff = (double)ctas / (double)(waves * num_sms);
         if (eff > best_eff + 1e-9) { best_eff = eff; best = ns; }
         if (eff >= 0.9) return ns;
     }
@@ -776,13 +765,13 @@ int choose_nsplit(long long items, int tiles_total) {
 struct DwPlan {
     int tiles_per_seq, tiles_total, nsplit, tiles_per_split;
 };
-DwPlan dw_plan(const flashmhf_dims &d) {
+DwPlan dw_plan(const flashmhf_dims &d, int num_sms) {
     DwPlan p;
     const int G = d.H / d.Hkuv;
     p.tiles_per_seq = (d.S + kBT - 1) / kBT;
     p.tiles_total = p.tiles_per_seq * G * d.B;
     const long long items = (long long)d.Hkuv * ((long long)d.E * d.De / kBI);
-    const int ns = choose_nsplit(items, p.tiles_total);
+    const int ns = choose_nsplit(items, p.tiles_total, num_sms);
     p.tiles_per_split = (p.tiles_total + ns - 1) / ns;
     p.nsplit = (p.tiles_total + p.tiles_per_split - 1) / p.tiles_per_split;  // no empty split
     return p;
@@ -791,6 +780,9 @@ DwPlan dw_plan(const flashmhf_dims &d) {
 template <int DH>
 int launch_bwd(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch) {
     const flashmhf_dims &d = p.d;
+    const DeviceCtl *dc = device_ctl();
+    if (!dc) return FLASHMHF_ERR_CUDA;
+    const bool want_inputs = (p.parts & FLASHMHF_BWD_INPUTS) != 0, want_weights = (p.parts & FLASHMHF_BWD_WEIGHTS) != 0;
     CUtensorMap tmQ, tmdO, tmK, tmU, tmV, tmdQ;
     int rc;
     if ((rc = encode_act_map(&tmQ, p.Q, d, kBT)) != 0) return rc;
@@ -798,63 +790,78 @@ int launch_bwd(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch) {
     if ((rc = encode_weight_map(&tmK, p.K, d, kBI)) != 0) return rc;
     if ((rc = encode_weight_map(&tmU, p.U, d, kBI)) != 0) return rc;
     if ((rc = encode_weight_map(&tmV, p.V, d, kBI)) != 0) return rc;
-    if ((rc = encode_act_map(&tmdQ, p.dQ, d, kBT)) != 0) return rc;
-    for (const flashmhf_tensor *t : {&p.dK, &p.dU, &p.dV}) {
-        if (d.E > 1 && t->stride[1] != (int64_t)d.De * t->stride[2]) return FLASHMHF_ERR_BAD_STRIDE;
-        if (t->stride[2] % 4 != 0 || t->stride[0] % 4 != 0) return FLASHMHF_ERR_BAD_STRIDE;
-    }
+    if (want_inputs && (rc = encode_act_map(&tmdQ, p.dQ, d, kBT)) != 0) return rc;
+    if (want_weights)
+        for (const flashmhf_tensor *t : {&p.dK, &p.dU, &p.dV}) {
+            if (d.E > 1 && t->stride[1] != (int64_t)d.De * t->stride[2]) return FLASHMHF_ERR_BAD_STRIDE;
+            if (t->stride[2] % 4 != 0 || t->stride[0] % 4 != 0) return FLASHMHF_ERR_BAD_STRIDE;
+        }
     cudaError_t e;
-    e = cudaFuncSetAttribute(bwd_dq_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DqSmem<DH>::kTotal);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(bwd_dw_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DwSmem<DH>::kTotal);
-    if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(bwd kernels)"); return FLASHMHF_ERR_CUDA; }
-
-    const int G = d.H / d.Hkuv;
-    DqArgs qa{static_cast<const float *>(p.R.ptr), p.R.stride[0], p.R.stride[1], p.R.stride[2],
-              static_cast<float *>(p.dR.ptr), p.dR.stride[0], p.dR.stride[1], p.dR.stride[2],
-              d.S, d.E, d.De, G, device_status_ptr()};
-    dim3 gq((d.S + kBT - 1) / kBT, d.H, d.B);
-    prof_mark(st, kMarkStart);
-    bwd_dq_kernel<DH><<<gq, kThreads, DqSmem<DH>::kTotal, st>>>(tmQ, tmdO, tmK, tmU, tmV, tmdQ, qa);
-    prof_mark(st, kMarkBwdDq);
-    *n_launch += 1;
-    if ((e = cudaGetLastError()) != cudaSuccess) { set_cuda_error(e, "bwd_dq_kernel launch"); return FLASHMHF_ERR_CUDA; }
-
-    const DwPlan pl = dw_plan(d);
-    DwArgs wa{static_cast<const float *>(p.R.ptr), p.R.stride[0], p.R.stride[1], p.R.stride[2],
-              static_cast<float *>(p.workspace), d.S, d.E, d.De, G, d.B, d.Hkuv,
-              pl.tiles_per_seq, pl.tiles_total, pl.tiles_per_split, device_status_ptr()};
-    dim3 gw(d.E * d.De / kBI, d.Hkuv, pl.nsplit);
-    bwd_dw_kernel<DH><<<gw, kThreads, DwSmem<DH>::kTotal, st>>>(tmQ, tmdO, tmK, tmU, tmV, wa);
-    prof_mark(st, kMarkBwdDw);
-    *n_launch += 1;
-    if ((e = cudaGetLastError()) != cudaSuccess) { set_cuda_error(e, "bwd_dw_kernel launch"); return FLASHMHF_ERR_CUDA; }
-
-    ReduceArgs ra;
-    ra.ws = static_cast<const float *>(p.workspace);
-    const flashmhf_tensor *outs[3] = {&p.dK, &p.dU, &p.dV};
-    for (int i = 0; i < 3; ++i) {
-        ra.out[i] = static_cast<__nv_bfloat16 *>(outs[i]->ptr);
-        ra.s_head[i] = outs[i]->stride[0];
-        ra.s_row[i] = outs[i]->stride[2];
+    {  // the attribute is per device and per kernel: set once for each pair
+        static std::atomic<bool> done[64];
+        if (!done[dc->device].load(std::memory_order_acquire)) {
+            e = cudaFuncSetAttribute(bwd_dq_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DqSmem<DH>::kTotal);
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(bwd_dw_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DwSmem<DH>::kTotal);
+            if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(bwd kernels)"); return FLASHMHF_ERR_CUDA; }
+            done[dc->device].store(true, std::memory_order_release);
+        }
     }
-    ra.I = d.E * d.De;
-    ra.DH = DH;
-    ra.plane = (long long)d.Hkuv * ra.I * DH;
-    ra.nsplit = pl.nsplit;
-    const long long n4 = 3 * ra.plane / 4;
-    const int blocks = (int)((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
-    dw_reduce_kernel<<<blocks, 256, 0, st>>>(ra);
-    prof_mark(st, kMarkBwdReduce);
-    *n_launch += 1;
-    if ((e = cudaGetLastError()) != cudaSuccess) { set_cuda_error(e, "dw_reduce_kernel launch"); return FLASHMHF_ERR_CUDA; }
+    const int G = d.H / d.Hkuv;
+    const float s0 = p.scale.head_scaling, c = p.scale.head_scaling * p.scale.up_scaling * p.scale.final_scaling;
+
+    // Weight gradients first: in data-parallel training their all-reduce can then start while dQ/dR still run.
+    if (want_weights) {
+        const DwPlan pl = dw_plan(d, dc->num_sms);
+        DwArgs wa{static_cast<const float *>(p.R.ptr), p.R.stride[0], p.R.stride[1], p.R.stride[2],
+                  static_cast<float *>(p.workspace), d.S, d.E, d.De, G, d.B, d.Hkuv,
+                  pl.tiles_per_seq, pl.tiles_total, pl.tiles_per_split, s0, c, wait_args(dc)};
+        dim3 gw(d.E * d.De / kBI, d.Hkuv, pl.nsplit);
+        prof_mark(st, kMarkStart);
+        bwd_dw_kernel<DH><<<gw, kThreads, DwSmem<DH>::kTotal, st>>>(tmQ, tmdO, tmK, tmU, tmV, wa);
+        prof_mark(st, kMarkBwdDw);
+        *n_launch += 1;
+        if ((e = cudaGetLastError()) != cudaSuccess) { set_cuda_error(e, "bwd_dw_kernel launch"); return FLASHMHF_ERR_CUDA; }
+
+        ReduceArgs ra;
+        ra.ws = static_cast<const float *>(p.workspace);
+        const flashmhf_tensor *outs[3] = {&p.dK, &p.dU, &p.dV};
+        for (int i = 0; i < 3; ++i) {
+            ra.out[i] = static_cast<__nv_bfloat16 *>(outs[i]->ptr);
+            ra.s_head[i] = outs[i]->stride[0];
+            ra.s_row[i] = outs[i]->stride[2];
+        }
+        ra.I = d.E * d.De;
+        ra.DH = DH;
+        ra.plane = (long long)d.Hkuv * ra.I * DH;
+        ra.nsplit = pl.nsplit;
+        const long long n4 = 3 * ra.plane / 4, cap = (long long)dc->num_sms * 8;
+        const int blocks = (int)((n4 + 255) / 256 < cap ? (n4 + 255) / 256 : cap);
+        dw_reduce_kernel<<<blocks, 256, 0, st>>>(ra);
+        prof_mark(st, kMarkBwdReduce);
+        *n_launch += 1;
+        if ((e = cudaGetLastError()) != cudaSuccess) { set_cuda_error(e, "dw_reduce_kernel launch"); return FLASHMHF_ERR_CUDA; }
+    }
+
+    if (want_inputs) {
+        DqArgs qa{static_cast<const float *>(p.R.ptr), p.R.stride[0], p.R.stride[1], p.R.stride[2],
+                  static_cast<float *>(p.dR.ptr), p.dR.stride[0], p.dR.stride[1], p.dR.stride[2],
+                  d.S, d.E, d.De, G, s0, c, wait_args(dc)};
+        dim3 gq((d.S + kBT - 1) / kBT, d.H, d.B);
+        prof_mark(st, kMarkStart);
+        bwd_dq_kernel<DH><<<gq, kThreads, DqSmem<DH>::kTotal, st>>>(tmQ, tmdO, tmK, tmU, tmV, tmdQ, qa);
+        prof_mark(st, kMarkBwdDq);
+        *n_launch += 1;
+        if ((e = cudaGetLastError()) != cudaSuccess) { set_cuda_error(e, "bwd_dq_kernel launch"); return FLASHMHF_ERR_CUDA; }
+    }
     return FLASHMHF_OK;
 }
 
 }  // namespace
 
 size_t tc_backward_workspace_bytes(const flashmhf_dims &d) {
-    const DwPlan pl = dw_plan(d);
+    const DeviceCtl *dc = device_ctl();
+    const DwPlan pl = dw_plan(d, dc ? dc->num_sms : 148);
     return (size_t)pl.nsplit * 3 * (size_t)d.Hkuv * (size_t)d.E * d.De * d.Dh * sizeof(float);
 }
 

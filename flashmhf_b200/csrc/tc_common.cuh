@@ -19,12 +19,12 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "kernels.h"
+
 namespace fmhf {
 
 // Status codes a kernel writes when a bounded wait runs out: kernel id * 100 + wait id.
-constexpr int kKernelFwd = 1, kKernelBwdDq = 2, kKernelBwdDw = 3;
-// ~1.5 s at 1.4-1.9 GHz; a healthy kernel waits microseconds.
-constexpr long long kWaitLimitCycles = 3LL << 30;
+constexpr int kKernelFwd = 1, kKernelBwdDq = 2, kKernelBwdDw = 3, kKernelSelfTest = 99;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -35,6 +35,23 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar) : "memory");
+}
+// One arrival on behalf of a whole warp whose 32 lanes have all finished the work the barrier guards: the lanes meet
+// first, so everything each of them did (and fenced) is ordered before the one arrival.  Barriers signalled this way
+// are initialised with the number of WARPS (kWarpArrive = 1) -- 32 times fewer arrivals on the same shared-memory word.
+#ifndef FMHF_LANE_ARRIVE
+constexpr int kWarpArrive = 1;
+#else
+constexpr int kWarpArrive = 0;
+#endif
+__host__ __device__ constexpr int arrivals_of(int threads) { return kWarpArrive ? threads / 32 : threads; }
+__device__ __forceinline__ void warp_arrive(uint32_t bar) {
+    if (kWarpArrive) {
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+    } else {
+        mbar_arrive(bar);
+    }
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar),
@@ -56,8 +73,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // teardown (which frees tensor memory).  The first failing wait also records its code globally.
 struct WaitCtl {
     volatile int *abort;  // in shared memory
-    int *status;          // in global memory
+    WaitArgs g;           // global status word, the launch's sequence number, the limit in cycles
 };
+// Was this launch already given up by one of its CTAs?  (read once per CTA, by the thread that sets `abort`)
+__device__ __forceinline__ int launch_aborted(const WaitArgs &g) {
+    return *reinterpret_cast<volatile unsigned *>(g.abort_seq) == g.seq;
+}
 
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtl &ctl, int code) {
     const long long t0 = clock64();
@@ -66,9 +87,10 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
         if (mbar_try_wait(bar, parity)) return true;
         if ((++it & 63u) == 0u) {
             if (*ctl.abort) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > ctl.g.limit_cycles) {
                 *ctl.abort = 1;
-                atomicCAS(ctl.status, 0, code);
+                atomicCAS(ctl.g.status, 0, code);
+                atomicExch(ctl.g.abort_seq, ctl.g.seq);
                 return false;
             }
         }
@@ -332,11 +354,11 @@ __device__ __forceinline__ uint32_t f2_to_bf16x2(f32x2 v) {
     return pack_bf16(a, b);
 }
 
-// Forward activation for two neighbouring columns: bf16x2 of  m * sigmoid(m) * n * r.
-// With t = tanh(m/2): m*sigmoid(m)*n*r = p + p*t, p = (m*n) * (r/2).   `half_r` = (r/2, r/2).
-__device__ __forceinline__ uint32_t fwd_act_pair(f32x2 m, f32x2 n, f32x2 half_r) {
-    const f32x2 half = f2_pack(0.5f, 0.5f);
-    const f32x2 t = f2_tanh(f2_mul(m, half));
+// Forward activation for two neighbouring columns: bf16x2 of  silu(s0 m) * (s1 n) * s2 * r  for raw products m, n.
+// With t = tanh(s0 m / 2): the value is p + p*t, p = (m*n) * (s0 s1 s2 r / 2).
+// `half_r` = (s0 s1 s2 r / 2) twice, `half_s0` = (s0 / 2) twice.
+__device__ __forceinline__ uint32_t fwd_act_pair(f32x2 m, f32x2 n, f32x2 half_r, f32x2 half_s0) {
+    const f32x2 t = f2_tanh(f2_mul(m, half_s0));
     const f32x2 p = f2_mul(f2_mul(m, n), half_r);
     return f2_to_bf16x2(f2_fma(p, t, p));
 }

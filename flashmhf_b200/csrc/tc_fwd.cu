@@ -23,24 +23,11 @@
 // token row of a block).
 //
 // Tensor memory (512 columns): O at [0, d_h), S buffers at [128, 256), [256, 384), [384, 512).
+#include <atomic>
+
 #include "kernels.h"
 #include "tc_common.cuh"
 #include "tensormap.cuh"
-
-#ifdef FMHF_TRACE
-// Debug build only: per-block clock stamps of CTA (1,0,0) for pipeline analysis.
-__device__ unsigned int g_fwd_trace[4][64][8];
-#define FMHF_TR(role, j, ev)                                                                   \
-    do {                                                                                       \
-        if (blockIdx.x == 1 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 64)                  \
-            g_fwd_trace[role][j][ev] = (unsigned int)clock64();                                 \
-    } while (0)
-extern "C" int flashmhf_debug_read_fwd_trace(unsigned int *out) {
-    return (int)cudaMemcpyFromSymbol(out, g_fwd_trace, sizeof(g_fwd_trace));
-}
-#else
-#define FMHF_TR(role, j, ev) do { } while (0)
-#endif
 
 namespace fmhf {
 namespace {
@@ -89,7 +76,9 @@ struct FwdArgs {
     int nsplit, blocks_per_split;
     float *part;           // [nsplit][B][H][S][DH] fp32, used when nsplit > 1
     int H;
-    int *status;
+    float half_s0;  // 0.5 * head_scaling: tanh argument scale, sigmoid(s0 m) = 0.5 + 0.5 tanh(0.5 s0 m)
+    float c;        // head_scaling * up_scaling * final_scaling, folded into the routing weight
+    WaitArgs wait;
 };
 
 // Ring position of block j in a ring of N slots: slot j % N and the parity of its lap.
@@ -124,11 +113,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     const int blocks_per_e = args.De / kBI;
     const int j0 = isplit * args.blocks_per_split;                          // first block of this CTA
     const int nblk = min(args.E * blocks_per_e - j0, args.blocks_per_split);  // blocks of this CTA (>= 1)
-    const WaitCtl ctl{abort_flag, args.status};
+    const WaitCtl ctl{abort_flag, args.wait};
     constexpr int W = kKernelFwd * 100;
 
     if (threadIdx.x == 0) {
-        *abort_flag = (*reinterpret_cast<volatile int *>(args.status) != 0);  // an earlier CTA gave up: drain fast
+        *abort_flag = launch_aborted(args.wait);  // a CTA of this launch gave up: drain fast
         mbar_init(bar(BAR_Q), 1);
         for (int i = 0; i < kRing; ++i) {
             mbar_init(bar(BAR_KUFULL + i), 1);
@@ -138,7 +127,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
         for (int i = 0; i < kSBars; ++i) {
             mbar_init(bar(BAR_SFULL + i), 1);
-            mbar_init(bar(BAR_AFULL + i), kGroupThreads);
+            mbar_init(bar(BAR_AFULL + i), arrivals_of(kGroupThreads));
             mbar_init(bar(BAR_SFREE + i), 1);
         }
         mbar_init(bar(BAR_OFULL), 1);
@@ -168,9 +157,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             RingPos<kRing> pk, pv;
             for (int j = 0; j < nblk + 2; ++j) {
                 if (j < nblk) {
-                    FMHF_TR(0, j, 0);
                     if (!mbar_wait(bar(BAR_KUEMPTY + pk.slot), pk.lap ^ 1, ctl, W + 1)) break;
-                    FMHF_TR(0, j, 1);
                     const uint32_t fku = bar(BAR_KUFULL + pk.slot), dku = sKU + pk.slot * L::kKUStage;
                     mbar_arrive_expect_tx(fku, L::kKUStage);
 #pragma unroll
@@ -211,11 +198,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             ps.advance(first);
             pf.advance(first + kDepth);
             for (int j = first; ok && j < nblk; j += 2) {
-                FMHF_TR(1, j, 0);
                 if (!mbar_wait(bar(BAR_KUFULL + pw.slot), pw.lap, ctl, W + 4)) break;
-                FMHF_TR(1, j, 1);
                 if (j >= kDepth && !mbar_wait(bar(BAR_SFREE + pf.slot), pf.lap, ctl, W + 5)) break;
-                FMHF_TR(1, j, 2);
                 tc_fence_after();
                 const uint64_t dku = dKU0 + pw.slot * kKUStep;
                 const uint32_t tS = tmem + kColS0 + (ps.slot >= kDepth ? ps.slot - kDepth : ps.slot) * kColSStride;
@@ -227,7 +211,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 }
                 umma_commit(bar(BAR_KUEMPTY + pw.slot));
                 umma_commit(bar(BAR_SFULL + ps.slot));
-                FMHF_TR(1, j, 3);
                 pw.advance(2);
                 ps.advance(2);
                 pf.advance(2);
@@ -247,7 +230,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             for (int j = 0; j < nblk; ++j) {
                 if (!mbar_wait(bar(BAR_VFULL + pw.slot), pw.lap, ctl, W + 6)) { ok = false; break; }
                 if (!mbar_wait(bar(BAR_AFULL + ps.slot), ps.lap, ctl, W + 7)) { ok = false; break; }
-                FMHF_TR(1, j, 4);
                 tc_fence_after();
                 const uint64_t dv = dV0 + pw.slot * kVStep;
                 const uint32_t tA = tmem + kColS0 + (ps.slot >= kDepth ? ps.slot - kDepth : ps.slot) * kColSStride;
@@ -256,7 +238,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                     umma_ts(tmem + kColO, tA + k * 8, dv + k * 128, idesc2, (j > 0 || k > 0) ? 1u : 0u);
                 umma_commit(bar(BAR_VEMPTY + pw.slot));
                 umma_commit(bar(BAR_SFREE + ps.slot));
-                FMHF_TR(1, j, 5);
                 pw.advance(1);
                 ps.advance(1);
             }
@@ -271,6 +252,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         const float *rrow = args.R + (long long)b * args.r_sb + (long long)h * args.r_sh + (long long)t * args.r_ss;
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
         bool ok = true;
+        const f32x2 half_s0 = f2_pack(args.half_s0, args.half_s0);
         // sub-network of this group's current block and position inside it; routing weight fetched a block ahead
         int e = (j0 + group) / blocks_per_e, in_e = (j0 + group) - e * blocks_per_e;
         float r_cur = (in_range && e < args.E) ? __ldg(rrow + e) : 0.f;
@@ -280,10 +262,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             int e_nb = e, in_nb = in_e + 2;  // where this group's next block lies
             while (in_nb >= blocks_per_e) { in_nb -= blocks_per_e; ++e_nb; }
             const float r_nb = (e_nb != e && in_range && e_nb < args.E) ? __ldg(rrow + e_nb) : r_cur;
-            const f32x2 half_r = f2_pack(0.5f * r_cur, 0.5f * r_cur);
-            FMHF_TR(2 + group, j, 0);
+            const float hr = 0.5f * args.c * r_cur;
+            const f32x2 half_r = f2_pack(hr, hr);
             if (!mbar_wait(bar(BAR_SFULL + p.slot), p.lap, ctl, W + 8)) { ok = false; break; }
-            FMHF_TR(2 + group, j, 1);
             tc_fence_after();
             const uint32_t ts = lane_base + kColS0 + (p.slot >= kDepth ? p.slot - kDepth : p.slot) * kColSStride;
             uint32_t a[32];  // 64 bf16 of this row of A
@@ -294,14 +275,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
 #pragma unroll
                 for (int i = 0; i < 16; ++i)
                     a[part * 16 + i] = fwd_act_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]),
-                                                    f2_pack_bits(n[2 * i], n[2 * i + 1]), half_r);
+                                                    f2_pack_bits(n[2 * i], n[2 * i + 1]), half_r, half_s0);
             }
-            FMHF_TR(2 + group, j, 3);
             tmem_st32(ts, a);  // over M[0:32] of this buffer, which is in registers by now
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(bar(BAR_AFULL + p.slot));
-            FMHF_TR(2 + group, j, 5);
+            warp_arrive(bar(BAR_AFULL + p.slot));
             p.advance(2);
             r_cur = r_nb;
             e = e_nb;
@@ -407,11 +386,11 @@ struct FwdPlan {
 };
 // With fewer token tiles than about half the SMs (decode-shaped calls) the blocks of the intermediate
 // dimension are spread over several CTAs per tile so that the weights stream in at full machine rate.
-FwdPlan fwd_plan(const flashmhf_dims &d) {
+FwdPlan fwd_plan(const flashmhf_dims &d, int num_sms) {
     const long long tiles = (long long)((d.S + kBT - 1) / kBT) * d.H * d.B;
     const int nblk = d.E * d.De / kBI;
     int ns = 1;
-    if (tiles < 74) ns = (int)((148 + tiles - 1) / tiles);
+    if (tiles < num_sms / 2) ns = (int)((num_sms + tiles - 1) / tiles);
     if (ns > nblk) ns = nblk;
     FwdPlan p;
     p.blocks_per_split = (nblk + ns - 1) / ns;
@@ -429,11 +408,17 @@ int launch_fwd(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
     if ((rc = encode_weight_map(&tmU, p.U, p.d, kBI)) != 0) return rc;
     if ((rc = encode_weight_map(&tmV, p.V, p.d, kBI)) != 0) return rc;
     if ((rc = encode_act_map(&tmO, p.O, p.d, kBT)) != 0) return rc;
-    {  // per device, so set on every call (cheap)
-        cudaError_t e = cudaFuncSetAttribute(fwd_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
-        if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(fwd_kernel)"); return FLASHMHF_ERR_CUDA; }
+    const DeviceCtl *dc = device_ctl();
+    if (!dc) return FLASHMHF_ERR_CUDA;
+    {  // the attribute is per device and per kernel: set once for each pair
+        static std::atomic<bool> done[64];
+        if (!done[dc->device].load(std::memory_order_acquire)) {
+            cudaError_t e = cudaFuncSetAttribute(fwd_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
+            if (e != cudaSuccess) { set_cuda_error(e, "cudaFuncSetAttribute(fwd_kernel)"); return FLASHMHF_ERR_CUDA; }
+            done[dc->device].store(true, std::memory_order_release);
+        }
     }
-    const FwdPlan pl = fwd_plan(p.d);
+    const FwdPlan pl = fwd_plan(p.d, dc->num_sms);
     if (pl.nsplit > 1) {
         if (!p.workspace || p.workspace_bytes < tc_forward_workspace_bytes(p.d) ||
             (reinterpret_cast<uintptr_t>(p.workspace) & 255u))
@@ -442,7 +427,8 @@ int launch_fwd(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
     }
     FwdArgs a{static_cast<const float *>(p.R.ptr), p.R.stride[0], p.R.stride[1], p.R.stride[2],
               p.d.S, p.d.E, p.d.De, p.d.H / p.d.Hkuv, pl.nsplit, pl.blocks_per_split,
-              static_cast<float *>(p.workspace), p.d.H, device_status_ptr()};
+              static_cast<float *>(p.workspace), p.d.H, 0.5f * p.scale.head_scaling,
+              p.scale.head_scaling * p.scale.up_scaling * p.scale.final_scaling, wait_args(dc)};
     dim3 grid(((p.d.S + kBT - 1) / kBT) * pl.nsplit, p.d.H, p.d.B);
     prof_mark(st, kMarkStart);
     fwd_kernel<DH><<<grid, kThreads, L::kTotal, st>>>(tmQ, tmK, tmU, tmV, tmO, a);
@@ -455,7 +441,8 @@ int launch_fwd(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
         OReduceArgs ra{static_cast<const float *>(p.workspace), plane, static_cast<__nv_bfloat16 *>(p.O.ptr),
                        p.O.stride[0], p.O.stride[1], p.O.stride[2], pl.nsplit, p.d.H, p.d.S, DH};
         const long long n4 = plane / 4;
-        const int blocks = (int)((n4 + 255) / 256 < 148 * 4 ? (n4 + 255) / 256 : 148 * 4);
+        const long long cap = (long long)dc->num_sms * 4;
+        const int blocks = (int)((n4 + 255) / 256 < cap ? (n4 + 255) / 256 : cap);
         o_reduce_kernel<<<blocks, 256, 0, st>>>(ra);
         prof_mark(st, kMarkFwdReduce);
         *n_launch += 1;
@@ -467,7 +454,8 @@ int launch_fwd(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
 }  // namespace
 
 size_t tc_forward_workspace_bytes(const flashmhf_dims &d) {
-    const FwdPlan pl = fwd_plan(d);
+    const DeviceCtl *dc = device_ctl();
+    const FwdPlan pl = fwd_plan(d, dc ? dc->num_sms : 148);
     if (pl.nsplit <= 1) return 0;
     return (size_t)pl.nsplit * (size_t)d.B * d.H * d.S * d.Dh * sizeof(float);
 }

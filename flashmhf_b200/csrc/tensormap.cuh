@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <string.h>
+
 #include "kernels.h"
 
 namespace fmhf {
@@ -28,8 +30,55 @@ inline EncodeTiledFn encode_tiled_fn() {
 // bf16 tensor, innermost dim contiguous, 128-byte swizzle, out-of-range elements read as zero and
 // are not written.  dims/box are innermost-first; stride_elems[i] is the element stride of dim i+1.
 // A dim of extent 1 may carry any stride; it is replaced by a legal one.
+//
+// Encoded maps are kept in a small per-thread cache keyed by (base, rank, dims, strides, box): a map depends on
+// nothing else, training and decode loops present the same tensors call after call, and the driver's encoder
+// costs more host time than the rest of a call.  Per thread, so no lock; 64 entries, replaced round-robin.
+struct MapKey {
+    const void *base;
+    int32_t rank;
+    uint32_t box[4];
+    uint64_t dims[4];
+    int64_t strides[3];
+};
+struct MapCache {
+    static constexpr int kEntries = 64;
+    MapKey key[kEntries];
+    CUtensorMap map[kEntries];
+    int used = 0, next = 0;
+};
+inline MapCache &map_cache() {
+    static thread_local MapCache c;
+    return c;
+}
+
+inline int encode_bf16_map_uncached(CUtensorMap *out, const void *base, int rank, const uint64_t *dims,
+                                    const int64_t *stride_elems, const uint32_t *box);
+
 inline int encode_bf16_map(CUtensorMap *out, const void *base, int rank, const uint64_t *dims,
                            const int64_t *stride_elems, const uint32_t *box) {
+    MapKey k;
+    memset(&k, 0, sizeof(k));
+    k.base = base;
+    k.rank = rank;
+    for (int i = 0; i < rank; ++i) { k.dims[i] = dims[i]; k.box[i] = box[i]; }
+    for (int i = 0; i + 1 < rank; ++i) k.strides[i] = stride_elems[i];
+    MapCache &c = map_cache();
+    for (int i = 0; i < c.used; ++i)
+        if (memcmp(&c.key[i], &k, sizeof(k)) == 0) {
+            *out = c.map[i];
+            return FLASHMHF_OK;
+        }
+    const int rc = encode_bf16_map_uncached(out, base, rank, dims, stride_elems, box);
+    if (rc != FLASHMHF_OK) return rc;
+    const int slot = c.used < MapCache::kEntries ? c.used++ : (c.next = (c.next + 1) % MapCache::kEntries);
+    c.key[slot] = k;
+    c.map[slot] = *out;
+    return FLASHMHF_OK;
+}
+
+inline int encode_bf16_map_uncached(CUtensorMap *out, const void *base, int rank, const uint64_t *dims,
+                                    const int64_t *stride_elems, const uint32_t *box) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) {
         set_cuda_error(cudaErrorUnknown, "cuTensorMapEncodeTiled entry point not found");

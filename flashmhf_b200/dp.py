@@ -44,6 +44,36 @@ def allreduce_weight_grads(grads, group=None, average=False):
     return grads
 
 
+class WeightGradBucket:
+    """dK, dU and dV as three views of ONE contiguous buffer, so that their exchange is one all-reduce with no packing
+    copy before it and no copy back after it: the backward kernels write straight into the views."""
+
+    def __init__(self, like):
+        """`like`: a K-shaped tensor ([H_kuv, E, d_e, d_h]); the views are contiguous tensors of that shape."""
+        n = like.numel()
+        self.flat = torch.empty(3 * n, dtype=like.dtype, device=like.device)
+        self.views = tuple(self.flat[i * n:(i + 1) * n].view(like.shape) for i in range(3))
+
+
+def exchange_under_inputs(weights_fn, inputs_fn, bucket, group=None, average=False):
+    """Backward of one layer with the gradient exchange hidden under half of it.
+
+    ``weights_fn(views)`` computes dK, dU, dV into ``bucket.views`` (first, although autograd order would put dQ first);
+    the all-reduce of the bucket starts as soon as that work is enqueued and runs while ``inputs_fn()`` computes dQ and
+    dR, which no other rank needs.  Returns what ``inputs_fn`` returns; on return the current stream has been made to wait
+    for the reduced bucket.  With one rank it just calls the two functions."""
+    weights_fn(bucket.views)
+    work = None
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        work = dist.all_reduce(bucket.flat, op=dist.ReduceOp.SUM, group=group, async_op=True)
+    out = inputs_fn()
+    if work is not None:
+        work.wait()
+        if average:
+            bucket.flat /= dist.get_world_size(group)
+    return out
+
+
 def max_over_ranks(value, device, group=None):
     """Largest value of a Python float across ranks (used for device-timed durations)."""
     t = torch.tensor([float(value)], dtype=torch.float64, device=device)

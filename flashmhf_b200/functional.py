@@ -64,20 +64,34 @@ def _dims(B, H, S, dh, hk, E, de, dtype):
     return _lib.Dims(B, H, S, dh, hk, E, de, _DT[dtype])
 
 
+def _scaling(scaling):
+    """(head_scaling, up_scaling, final_scaling) of the eager layer (modeling_mhffnmoe.py:270-279) -> C struct."""
+    hs, us, fs = (float(v) for v in scaling)
+    for v in (hs, us, fs):
+        if v == 0.0 or v != v or v in (float("inf"), float("-inf")):
+            raise ValueError(f"scaling constants must be finite and non-zero, got {tuple(scaling)}")
+    return _lib.Scaling(hs, us, fs)
+
+
+def _routing(R):
+    """R as the kernels read it: fp32, unit inner stride, 4-byte aligned (any outer strides)."""
+    R = R.to(torch.float32)
+    return R if R.stride(-1) == 1 or R.size(-1) == 1 else R.contiguous()
+
+
 def _tokens_as_sequence(*ts):
     """Decode-shaped call (S == 1, B > 1): view [B,H,1,X] tensors as [1,H,B,X] -- a pure permutation, no copy --
     so that the B token rows share tiles instead of occupying one 128-row tile each."""
     return [t.permute(2, 1, 0, 3) for t in ts]
 
 
-def forward_raw(Q, K, U, V, R, out=None):
+def forward_raw(Q, K, U, V, R, out=None, scaling=_lib.NO_SCALING):
     """O = flashmhf_forward(...) on the current stream; no autograd."""
     B, H, S, dh, hk, E, de = _validate(Q, K, U, V, R)
     lib = _lib.load()
+    sc = _scaling(scaling)
     Q, K, U, V = _prep(Q), _prep(K, True, de), _prep(U, True, de), _prep(V, True, de)
-    R = R.to(torch.float32)
-    if R.stride(-1) != 1:
-        R = R.contiguous()
+    R = _routing(R)
     O = torch.empty_like(Q) if out is None else out  # keeps Q's memory layout ([B,H,S,d] or [B,S,H,d])
     Qk, Rk, Ok = Q, R, O
     if S == 1 and B > 1:
@@ -90,54 +104,87 @@ def forward_raw(Q, K, U, V, R, out=None):
     nbytes = int(lib.flashmhf_forward_workspace_bytes(C.byref(d)))
     ws = torch.empty(nbytes, dtype=torch.uint8, device=Q.device) if nbytes else None
     p = _lib.FwdParams(d, _tensor(Qk), _tensor(K), _tensor(U), _tensor(V), _tensor(Rk), _tensor(Ok),
-                       ws.data_ptr() if nbytes else None, nbytes)
+                       ws.data_ptr() if nbytes else None, nbytes, sc)
     with torch.cuda.device(Q.device):
         _lib.check(lib.flashmhf_forward(C.byref(p), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return O
 
 
-def backward_raw(Q, K, U, V, R, dO):
-    """(dQ, dK, dU, dV, dR) = flashmhf_backward(...) on the current stream; no autograd."""
+def backward_raw(Q, K, U, V, R, dO, scaling=_lib.NO_SCALING, parts="all", weight_grads=None):
+    """(dQ, dK, dU, dV, dR) = flashmhf_backward(...) on the current stream; no autograd.
+
+    ``parts``: "all", or "weights" (dK, dU, dV only; dQ and dR come back as None) or "inputs" (the reverse) --
+    data-parallel training runs the weights part first and overlaps its all-reduce with the inputs part.
+    ``weight_grads``: optional (dK, dU, dV) tensors to write into (e.g. three views of one all-reduce bucket)."""
     B, H, S, dh, hk, E, de = _validate(Q, K, U, V, R)
     if dO.shape != Q.shape:
         raise AssertionError("grad_output shape should be the same as Q")
+    if parts not in ("all", "weights", "inputs"):
+        raise ValueError(f"parts must be 'all', 'weights' or 'inputs', got {parts!r}")
     lib = _lib.load()
+    sc = _scaling(scaling)
     Q, K, U, V = _prep(Q), _prep(K, True, de), _prep(U, True, de), _prep(V, True, de)
     dO = _prep(dO.to(Q.dtype))
-    R = R.to(torch.float32)
-    if R.stride(-1) != 1:
-        R = R.contiguous()
-    dQ = torch.empty_like(Q)  # keeps Q's memory layout
-    # weight gradients in the weights' own memory layout (the layer passes strided views of [I, H_kuv*d_h] parameters:
-    # their gradients then need no re-layout copy); the fp32 check kernels write contiguous outputs
-    fmt = torch.preserve_format if Q.dtype == torch.bfloat16 else torch.contiguous_format
-    dK, dU, dV = (torch.empty_like(t, memory_format=fmt) for t in (K, U, V))
-    dR = torch.empty((B, H, S, E), dtype=torch.float32, device=Q.device)
+    R = _routing(R)
+    none = _lib.Tensor(None, (C.c_int64 * 3)(0, 0, 0))
+    dQ = dR = dK = dU = dV = None
+    tQ = tR = tK = tU = tV = none
+    ws_ptr, nbytes = None, 0
     d = _dims(B, H, S, dh, hk, E, de, Q.dtype)
-    nbytes = int(lib.flashmhf_backward_workspace_bytes(C.byref(d)))
-    ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=Q.device)
-    p = _lib.BwdParams(d, _tensor(Q), _tensor(K), _tensor(U), _tensor(V), _tensor(R), _tensor(dO), _tensor(dQ),
-                       _tensor(dK), _tensor(dU), _tensor(dV), _tensor(dR), ws.data_ptr(), nbytes)
+    if parts != "weights":
+        dQ = torch.empty_like(Q)  # keeps Q's memory layout
+        dR = torch.empty((B, H, S, E), dtype=torch.float32, device=Q.device)
+        tQ, tR = _tensor(dQ), _tensor(dR)
+    if parts != "inputs":
+        if weight_grads is not None:
+            dK, dU, dV = weight_grads
+            for g, w in ((dK, K), (dU, U), (dV, V)):
+                if g.shape != w.shape or g.dtype != w.dtype or g.device != w.device:
+                    raise ValueError("weight_grads must match K, U, V in shape, dtype and device")
+        else:
+            # in the weights' own memory layout (the layer passes strided views of [I, H_kuv*d_h] parameters: their
+            # gradients then need no re-layout copy); the fp32 check kernels write contiguous outputs
+            fmt = torch.preserve_format if Q.dtype == torch.bfloat16 else torch.contiguous_format
+            dK, dU, dV = (torch.empty_like(t, memory_format=fmt) for t in (K, U, V))
+        tK, tU, tV = _tensor(dK), _tensor(dU), _tensor(dV)
+        nbytes = int(lib.flashmhf_backward_workspace_bytes(C.byref(d)))
+        ws = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=Q.device)
+        ws_ptr = ws.data_ptr()
+    mask = {"all": 0, "inputs": _lib.BWD_INPUTS, "weights": _lib.BWD_WEIGHTS}[parts]
+    p = _lib.BwdParams(d, _tensor(Q), _tensor(K), _tensor(U), _tensor(V), _tensor(R), _tensor(dO), tQ, tK, tU, tV, tR,
+                       ws_ptr, nbytes, sc, mask)
     with torch.cuda.device(Q.device):
         _lib.check(lib.flashmhf_backward(C.byref(p), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return dQ, dK, dU, dV, dR
 
 
 class FlashMHFFunction(torch.autograd.Function):
-    """forward(ctx, Q, K, U, V, R) -> O ; backward(ctx, dO) -> dQ, dK, dU, dV, dR."""
+    """forward(ctx, Q, K, U, V, R[, head_scaling, up_scaling, final_scaling]) -> O ;
+    backward(ctx, dO) -> dQ, dK, dU, dV, dR (and None for the three constants).
+
+    The constants are those of the reference's eager loop (models/flashmhf/modeling_mhffnmoe.py:270-279, 420-425);
+    its own flash path has none (kernels/triton/flash_mlp_moe.py:741), which is the default of 1."""
 
     @staticmethod
-    def forward(ctx, Q, K, U, V, R):
-        O = forward_raw(Q, K, U, V, R)
+    def forward(ctx, Q, K, U, V, R, head_scaling=1.0, up_scaling=1.0, final_scaling=1.0):
+        ctx.scaling = (float(head_scaling), float(up_scaling), float(final_scaling))
+        O = forward_raw(Q, K, U, V, R, scaling=ctx.scaling)
         ctx.save_for_backward(Q, K, U, V, R)
         return O
 
     @staticmethod
     def backward(ctx, grad_output):
         Q, K, U, V, R = ctx.saved_tensors
-        dQ, dK, dU, dV, dR = backward_raw(Q, K, U, V, R, grad_output)
-        return dQ, dK, dU, dV, dR.to(R.dtype)
+        dQ, dK, dU, dV, dR = backward_raw(Q, K, U, V, R, grad_output, scaling=ctx.scaling)
+        return dQ, dK, dU, dV, dR.to(R.dtype), None, None, None
 
 
-def flash_mhf(Q, K, U, V, R):
-    return FlashMHFFunction.apply(Q, K, U, V, R)
+def flash_mhf(Q, K, U, V, R, head_scaling=1.0, up_scaling=1.0, final_scaling=1.0):
+    return FlashMHFFunction.apply(Q, K, U, V, R, head_scaling, up_scaling, final_scaling)
+
+
+def check_device_status():
+    """Synchronise and raise FlashMHFError if a kernel of this library gave up on a bounded wait (its outputs are then
+    unwritten).  The entry points only enqueue work, so this is the place a host loop learns of it: call it where the
+    loop synchronises anyway (after the loss is read back, at the end of a step)."""
+    _lib.device_status()

@@ -101,13 +101,16 @@ def expert_views(gate_weight, up_weight, down_weight, Hkuv, E):
     return f(gate_weight), f(up_weight), f(down_weight)
 
 
-def mhffn_layer(x, p, *, H, Hkuv, E, apply_rmsnorm, eps=1e-5):
-    """y = w_self_2(op(prologue(w_self(x)))) for bf16 CUDA tensors; p holds the reference's parameter names."""
+def mhffn_layer(x, p, *, H, Hkuv, E, apply_rmsnorm, eps=1e-5, head_scaling=1.0, up_scaling=1.0, final_scaling=1.0):
+    """y = w_self_2(op(prologue(w_self(x)))) for bf16 CUDA tensors; p holds the reference's parameter names
+    (optionally ``w_self_bias`` / ``w_self_2_bias``, the biases the reference creates with config.mlp_bias).
+    The three constants are the eager layer's (models/flashmhf/modeling_mhffnmoe.py:270-279); every shipped
+    configuration leaves them at 1."""
     B, S, hid = x.shape
-    q_lin = F.linear(x, p["w_self"]) if p.get("w_self") is not None else x
+    q_lin = F.linear(x, p["w_self"], p.get("w_self_bias")) if p.get("w_self") is not None else x
     prologue = fused_prologue if E <= 32 else torch_prologue
     Q, R = prologue(q_lin, p["q_norm"] if apply_rmsnorm else None, p["router"], eps)
     K, U, V = expert_views(p["gate_weight"], p["up_weight"], p["down_weight"], Hkuv, E)
-    O = flash_mhf(Q, K, U, V, R)                      # [B,H,S,d_h] view of [B,S,H,d_h] memory
+    O = flash_mhf(Q, K, U, V, R, head_scaling, up_scaling, final_scaling)  # [B,H,S,d_h] view of [B,S,H,d_h] memory
     O = O.transpose(1, 2).reshape(B, S, hid)          # no copy when O kept Q's layout
-    return F.linear(O, p["w_self_2"]) if p.get("w_self_2") is not None else O
+    return F.linear(O, p["w_self_2"], p.get("w_self_2_bias")) if p.get("w_self_2") is not None else O

@@ -36,6 +36,7 @@ class LMConfig:
     rms_norm_eps: float = 1e-5
     rope_theta: float = 10000.0
     tie_word_embeddings: bool = False
+    mlp_bias: bool = False                  # bias of w_self / w_self_2 (modeling_mhffnmoe.py:337-338); off in every shipped config
 
     @staticmethod
     def lm_370m():
@@ -151,8 +152,8 @@ class MHFFN(nn.Module):
         H, Hk, hid, I = cfg.mhffnmoe_num_heads, cfg.mhffnmoe_num_kuv_heads, cfg.hidden_size, cfg.intermediate_size
         dh = hid // H
         if not cfg.mhffnmoe_skip_linear:
-            self.w_self = nn.Linear(hid, hid, bias=False)
-            self.w_self_2 = nn.Linear(hid, hid, bias=False)
+            self.w_self = nn.Linear(hid, hid, bias=cfg.mlp_bias)
+            self.w_self_2 = nn.Linear(hid, hid, bias=cfg.mlp_bias)
         else:
             self.w_self = self.w_self_2 = None
         self.gate_weight = nn.Parameter(torch.empty(I, dh * Hk))
@@ -167,6 +168,8 @@ class MHFFN(nn.Module):
              "w_self_2": None if self.w_self_2 is None else self.w_self_2.weight,
              "gate_weight": self.gate_weight, "up_weight": self.up_weight, "down_weight": self.down_weight,
              "router": self.router, "q_norm": self.q_norm.weight}
+        if self.w_self is not None and self.w_self.bias is not None:
+            p["w_self_bias"], p["w_self_2_bias"] = self.w_self.bias, self.w_self_2.bias
         return self.ffn(x, p, H=c.mhffnmoe_num_heads, Hkuv=c.mhffnmoe_num_kuv_heads, E=c.mhffnmoe_num_experts,
                         apply_rmsnorm=c.mhffnmoe_apply_rmsnorm, eps=c.rms_norm_eps)
 

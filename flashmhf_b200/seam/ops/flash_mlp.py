@@ -11,10 +11,11 @@ class FlashMLP(torch.nn.Module):
     def forward(self, Q, K, U, V, apply_dot_scaling=False, head_scaling=1.0, up_scaling=1.0, activation_fn="silu"):
         if activation_fn != "silu":
             raise ValueError("FlashMLP currently supports only SiLU activation")
-        if apply_dot_scaling or head_scaling != 1.0 or up_scaling != 1.0:
-            raise ValueError("FlashMLP does not support dot scaling")
+        # The reference's legacy module rejects dot scaling (kernels/triton/flash_mlp.py:1056-1057); its eager layer
+        # applies it (models/flashmhf/modeling_mhffnmoe.py:420-422).  Here the operator takes the two constants, so the
+        # legacy flash branch gives what the eager branch gives; final_scaling stays with the caller (modeling:403).
         if U is None:
             raise ValueError("FlashMLP SiLU variant requires up-projection tensor U (got None)")
         B, H, S, _ = Q.shape
         R = torch.ones(B, H, S, 1, dtype=torch.float32, device=Q.device)
-        return flash_mhf(Q, K.unsqueeze(1), U.unsqueeze(1), V.unsqueeze(1), R)
+        return flash_mhf(Q, K.unsqueeze(1), U.unsqueeze(1), V.unsqueeze(1), R, float(head_scaling), float(up_scaling), 1.0)

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define FLASHMHF_ABI_VERSION 2
+#define FLASHMHF_ABI_VERSION 3
 
 typedef enum flashmhf_status {
     FLASHMHF_OK = 0,
@@ -65,12 +65,26 @@ typedef struct flashmhf_dims {
     int32_t dtype;            /* flashmhf_dtype */
 } flashmhf_dims;
 
+/* The three constants of the reference's eager loop (models/flashmhf/modeling_mhffnmoe.py:270-279, 420-425):
+ *   O = sum_e R_e * final_scaling * ((SiLU(head_scaling * Q K_e^T) * (up_scaling * Q U_e^T)) V_e).
+ * Each must be finite and non-zero (else FLASHMHF_ERR_BAD_SHAPE); the layer uses head_scaling = up_scaling in
+ * {1, sqrt(H), H} and final_scaling in {1, sqrt(3/8)}. */
+typedef struct flashmhf_scaling {
+    float head_scaling, up_scaling, final_scaling;
+} flashmhf_scaling;
+
+/* flashmhf_bwd_params.parts: which gradients a backward call produces.  Data-parallel training calls the
+ * weights part first, starts the all-reduce of dK, dU, dV, and runs the inputs part under it. */
+#define FLASHMHF_BWD_INPUTS 1u   /* dQ and dR (dK, dU, dV, workspace may then be left unset) */
+#define FLASHMHF_BWD_WEIGHTS 2u  /* dK, dU and dV (dQ, dR may then be left unset) */
+
 typedef struct flashmhf_fwd_params {
     flashmhf_dims d;
     flashmhf_tensor Q, K, U, V, R; /* inputs */
     flashmhf_tensor O;             /* output, every element written; no pre-zeroing needed */
     void *workspace;               /* device scratch, 256-byte aligned; needed only when                 */
     size_t workspace_bytes;        /* flashmhf_forward_workspace_bytes() > 0 (short token counts), else NULL/0 */
+    flashmhf_scaling scale;        /* the eager layer's three constants; {1,1,1} for every shipped configuration */
 } flashmhf_fwd_params;
 
 typedef struct flashmhf_bwd_params {
@@ -79,6 +93,8 @@ typedef struct flashmhf_bwd_params {
     flashmhf_tensor dQ, dK, dU, dV, dR; /* outputs, every element written; dR is fp32 */
     void *workspace;                    /* device scratch, 256-byte aligned, contents undefined on entry and exit */
     size_t workspace_bytes;
+    flashmhf_scaling scale;             /* as in the forward call */
+    uint32_t parts;                     /* 0 = everything; else a mask of FLASHMHF_BWD_INPUTS | FLASHMHF_BWD_WEIGHTS */
 } flashmhf_bwd_params;
 
 /* ABI version of the loaded library (== FLASHMHF_ABI_VERSION of the header it was built from).
@@ -131,6 +147,9 @@ int flashmhf_backward(const flashmhf_bwd_params *p, void *stream);
  *     kernels overwrite everything they later read, so stale contents are harmless, but two calls
  *     whose kernels overlap on the GPU (different streams, no ordering between them) race on it:
  *     order them, or use flashmhf_backward with separate workspaces.
+ *   - Make the first call on each device outside any stream capture (the address look-up is not a
+ *     stream operation).  The address is cached per device ordinal for the life of the process and is
+ *     not refreshed after a cudaDeviceReset(): do not reset a device this library has been used on.
  * This entry point has no counterpart in the reference. */
 int flashmhf_backward_static_scratch(const flashmhf_bwd_params *p, void *stream);
 
@@ -190,9 +209,22 @@ int flashmhf_lm_rmsnorm_backward(const void *x, const float *w, const void *g, v
                                  size_t workspace_bytes, int64_t rows, int32_t n, float eps, void *stream);
 
 /* SYNCHRONOUS.  Waits for the current device, then reads and clears the status word the kernels
- * write when a bounded wait runs out.  *code = 0 if none did; otherwise a kernel/role identifier,
- * and the call returns FLASHMHF_ERR_DEVICE_TIMEOUT.  Reference counterpart: none. */
+ * write when a bounded wait runs out.  *code = 0 if none did; otherwise a kernel/role identifier
+ * (kernel * 100 + wait), and the call returns FLASHMHF_ERR_DEVICE_TIMEOUT.
+ * Semantics of a run-out wait: every mbarrier wait in the kernels is bounded (about 1.5 s); the launch
+ * whose wait ran out returns early through its normal teardown and leaves its outputs UNWRITTEN, its
+ * remaining CTAs drain at once, and the first code is kept in the word until this call reads it.  Later
+ * launches are not affected: they run normally whether or not the word has been read.  Because the
+ * entry points only enqueue work they cannot report the condition themselves; call this wherever the
+ * host already synchronises (after reading back a loss, at the end of a step).
+ * Reference counterpart: none. */
 int flashmhf_device_status(int *code);
+
+/* Self-test of the bounded-wait path: one small kernel waits, for at most `limit_cycles` SM clock
+ * cycles, on a barrier that nothing ever arrives at, records code 9901 in the status word and returns
+ * through the same teardown the operator kernels use.  Nothing faults or hangs; the next
+ * flashmhf_device_status() reports FLASHMHF_ERR_DEVICE_TIMEOUT with that code.  Reference counterpart: none. */
+int flashmhf_selftest_bounded_wait(long long limit_cycles, void *stream);
 
 /* Profiling aid.  Between flashmhf_profile_begin and flashmhf_profile_end every forward/backward
  * call records a CUDA event on its stream before its first kernel and after each kernel (no

@@ -35,8 +35,9 @@ def repeat_kuv(w: torch.Tensor, n_rep: int) -> torch.Tensor:
     return w[:, None].expand(hk, n_rep, e, de, dh).reshape(hk * n_rep, e, de, dh)
 
 
-def mhffn_forward(Q, K, U, V, R, *, out_dtype=None):
-    """O = sum_e R_e * ((silu(Q K_e^T) * (Q U_e^T)) V_e), evaluated the way the eager layer does.
+def mhffn_forward(Q, K, U, V, R, *, out_dtype=None, head_scaling=1.0, up_scaling=1.0, final_scaling=1.0):
+    """O = sum_e R_e * ((silu(Q K_e^T) * (Q U_e^T)) V_e), evaluated the way the eager layer does, including its
+    three constants (modeling_mhffnmoe.py:270-279; applied at :420, :422, :425; 1 in every shipped configuration).
 
     Q [B,H,S,d_h]; K,U,V [H_kuv,E,d_e,d_h]; R [B,H,S,E].  Every matmul runs in the dtype of Q
     (so bf16 inputs round every intermediate to bf16, as the eager path does); the sum over
@@ -50,14 +51,16 @@ def mhffn_forward(Q, K, U, V, R, *, out_dtype=None):
     acc_dtype = torch.float64 if Q.dtype == torch.float64 else torch.float32
     out = torch.zeros(Q.shape, dtype=acc_dtype, device=Q.device)
     for e in range(E):
-        w = F.silu(Q @ K[:, e].transpose(1, 2))
-        w = w * (Q @ U[:, e].transpose(1, 2))
-        out += (w @ V[:, e]).to(acc_dtype) * R[..., e:e + 1].to(acc_dtype)
+        w = F.silu(Q @ K[:, e].transpose(1, 2) * head_scaling)
+        w = w * (Q @ U[:, e].transpose(1, 2) * up_scaling)
+        out += (w @ V[:, e] * final_scaling).to(acc_dtype) * R[..., e:e + 1].to(acc_dtype)
     return out.to(out_dtype if out_dtype is not None else Q.dtype)
 
 
-def mhffn_backward(Q, K, U, V, R, dO):
+def mhffn_backward(Q, K, U, V, R, dO, *, head_scaling=1.0, up_scaling=1.0, final_scaling=1.0):
     """Explicit gradients of ``mhffn_forward`` for upstream gradient dO; returns (dQ,dK,dU,dV,dR).
+    With the constants s0, s1, s2 (head, up, final): M = s0 Q K^T, N = s1 Q U^T, dA = s2 dO V^T, and the
+    chain rule hands s0 to dM, s1 to dN and s2 to the A that multiplies dO in dV.
 
     Per expert e with r = R[..., e]:  M = Q K_e^T, N = Q U_e^T, sg = sigmoid(M), s = M*sg,
     dA = dO V_e^T, dR_e = rowsum(dA*s*N), dM = dA*(r*N)*(sg + s*(1-sg)), dN = dA*s*r,
@@ -74,18 +77,18 @@ def mhffn_backward(Q, K, U, V, R, dO):
     dR = torch.zeros(R.shape, dtype=Q.dtype, device=Q.device)
     for e in range(E):
         r = R[..., e:e + 1].to(Q.dtype)
-        M = Q @ Kr[:, e].transpose(1, 2)
-        N = Q @ Ur[:, e].transpose(1, 2)
+        M = Q @ Kr[:, e].transpose(1, 2) * head_scaling
+        N = Q @ Ur[:, e].transpose(1, 2) * up_scaling
         sg = torch.sigmoid(M)
         s = M * sg
-        dA = dO @ Vr[:, e].transpose(1, 2)
+        dA = dO @ Vr[:, e].transpose(1, 2) * final_scaling
         dR[..., e] = (dA * s * N).sum(-1)
-        dM = dA * (r * N) * (sg + s * (1 - sg))
-        dN = dA * s * r
+        dM = dA * (r * N) * (sg + s * (1 - sg)) * head_scaling
+        dN = dA * s * r * up_scaling
         dQ += dM @ Kr[:, e] + dN @ Ur[:, e]
         dKr[:, e] = (dM.transpose(2, 3) @ Q).sum(0)
         dUr[:, e] = (dN.transpose(2, 3) @ Q).sum(0)
-        dVr[:, e] = ((s * N * r).transpose(2, 3) @ dO).sum(0)
+        dVr[:, e] = ((s * N * r * final_scaling).transpose(2, 3) @ dO).sum(0)
     if g > 1:
         fold = lambda t: t.view(hk, g, E, de, dh).sum(1)
         dKr, dUr, dVr = fold(dKr), fold(dUr), fold(dVr)
@@ -97,19 +100,20 @@ class _OracleOp(torch.autograd.Function):
     so a layer-level gradient comparison with the reference exercises ``mhffn_backward``."""
 
     @staticmethod
-    def forward(ctx, Q, K, U, V, R):
+    def forward(ctx, Q, K, U, V, R, hs, us, fs):
         ctx.save_for_backward(Q, K, U, V, R)
-        return mhffn_forward(Q, K, U, V, R)
+        ctx.kw = dict(head_scaling=hs, up_scaling=us, final_scaling=fs)
+        return mhffn_forward(Q, K, U, V, R, **ctx.kw)
 
     @staticmethod
     def backward(ctx, dO):
         Q, K, U, V, R = ctx.saved_tensors
-        dQ, dK, dU, dV, dR = mhffn_backward(Q, K, U, V, R, dO.to(Q.dtype))
-        return dQ, dK, dU, dV, dR.to(R.dtype)
+        dQ, dK, dU, dV, dR = mhffn_backward(Q, K, U, V, R, dO.to(Q.dtype), **ctx.kw)
+        return dQ, dK, dU, dV, dR.to(R.dtype), None, None, None
 
 
-def oracle_op(Q, K, U, V, R):
-    return _OracleOp.apply(Q, K, U, V, R)
+def oracle_op(Q, K, U, V, R, head_scaling=1.0, up_scaling=1.0, final_scaling=1.0):
+    return _OracleOp.apply(Q, K, U, V, R, head_scaling, up_scaling, final_scaling)
 
 
 def router_weights(Q, router):
@@ -140,7 +144,7 @@ def split_heads(x_proj, gate_w, up_w, down_w, H, Hkuv, E):
     return Q, f(gate_w), f(up_w), f(down_w)
 
 
-def mhffn_layer_forward(x, p, *, H, Hkuv, E, apply_rmsnorm, eps, op=None):
+def mhffn_layer_forward(x, p, *, H, Hkuv, E, apply_rmsnorm, eps, op=None, scaling=(1.0, 1.0, 1.0)):
     """The whole FFN layer around the operator.
 
     p: dict with w_self [hid,hid], w_self_2 [hid,hid], gate_weight/up_weight/down_weight
@@ -150,16 +154,16 @@ def mhffn_layer_forward(x, p, *, H, Hkuv, E, apply_rmsnorm, eps, op=None):
     B, S, hid = x.shape
     dh = hid // H
     I = p["gate_weight"].shape[0]
-    q = F.linear(x, p["w_self"]).view(B, S, H, dh)
+    q = F.linear(x, p["w_self"], p.get("w_self_bias")).view(B, S, H, dh)
     if apply_rmsnorm:
         q = multihead_rmsnorm(q, p["q_norm"], eps)
     Q = q.transpose(1, 2).contiguous()
     f = lambda w: w.view(I, Hkuv, dh).transpose(0, 1).reshape(Hkuv, E, I // E, dh).contiguous()
     K, U, V = f(p["gate_weight"]), f(p["up_weight"]), f(p["down_weight"])
     R = router_weights(Q, p["router"])
-    O = op(Q, K, U, V, R.contiguous())
+    O = op(Q, K, U, V, R.contiguous(), *scaling) if tuple(scaling) != (1.0, 1.0, 1.0) else op(Q, K, U, V, R.contiguous())
     O = O.transpose(1, 2).contiguous().view(B, S, hid)
-    return F.linear(O, p["w_self_2"])
+    return F.linear(O, p["w_self_2"], p.get("w_self_2_bias"))
 
 
 def rel_l2(a, b):

@@ -73,11 +73,17 @@ class Recorder(torch.nn.Module):
         return torch.zeros_like(Q)
 
 
-def run_case(C, M, name, *, hidden, inter, H, Hkuv, E, B, S, rmsnorm, seed, full, skip_linear=False):
+def run_case(C, M, name, *, hidden, inter, H, Hkuv, E, B, S, rmsnorm, seed, full, skip_linear=False, scaled=False,
+             big=False):
+    """full: store every parameter and gradient (else only two moments of each gradient; parameters come from the seed).
+    scaled: turn on the layer's dot scaling (head/up = sqrt(H)) and final scaling (sqrt(3/8)).
+    big: a full-size case -- x and the loss weights are not stored (they come from the seed), dx is stored for every
+    fourth token only."""
     cfg = C.MHFFNMoEConfig(hidden_size=hidden, intermediate_size=inter, num_attention_heads=max(1, hidden // 64),
                            mhffnmoe_num_heads=H, mhffnmoe_num_kuv_heads=Hkuv, mhffnmoe_num_experts=E,
                            mhffnmoe_use_flash=False, mhffnmoe_custom_init=True, mhffnmoe_apply_rmsnorm=rmsnorm,
-                           mhffnmoe_skip_linear=skip_linear,
+                           mhffnmoe_skip_linear=skip_linear, mhffnmoe_apply_dot_scaling=scaled,
+                           mhffnmoe_apply_final_scaling=scaled,
                            rms_norm_eps=1e-5)
     layer = M.MHFFNMoEMultiHeadFFNFlash(cfg, use_flash=False)
     seeded_params(layer, seed)
@@ -87,6 +93,10 @@ def run_case(C, M, name, *, hidden, inter, H, Hkuv, E, B, S, rmsnorm, seed, full
     y = layer(x)
     (y * wloss).sum().backward()
     out = {"x": x.detach(), "wloss": wloss, "y": y.detach(), "dx": x.grad}
+    if big:
+        out = {"y": y.detach(), "dx_every4": x.grad[:, ::4].contiguous()}
+    hs, us, fs = float(layer.head_scaling), float(layer.up_scaling), float(layer.final_scaling)
+    out["scaling"] = np.array([hs, us, fs], dtype=np.float64)
     for n, p in layer.named_parameters():
         key = n.replace(".weight", "").replace(".", "_")
         if p.grad is None:  # q_norm when the per-head RMSNorm is off
@@ -107,8 +117,8 @@ def run_case(C, M, name, *, hidden, inter, H, Hkuv, E, B, S, rmsnorm, seed, full
     Kr, Ur, Vr = (M.repeat_kuv(t, H // Hkuv) for t in (K, U, V))
     O = torch.zeros(Q.shape, dtype=torch.float32)
     for i in range(E):  # the eager expression, evaluated with the reference's own helper for the head repeat
-        w = torch.nn.functional.silu(Q @ Kr[:, i].transpose(1, 2)) * (Q @ Ur[:, i].transpose(1, 2))
-        O += (w @ Vr[:, i]).float() * R[..., i:i + 1]
+        w = torch.nn.functional.silu(Q @ Kr[:, i].transpose(1, 2) * hs) * (Q @ Ur[:, i].transpose(1, 2) * us)
+        O += (w @ Vr[:, i] * fs).float() * R[..., i:i + 1]
     if full:
         out.update(op_Q=Q, op_K=K, op_U=U, op_V=V, op_R=R, op_O=O)
     else:
@@ -133,6 +143,12 @@ def main():
     run_case(C, M, "layer_128m_dims", hidden=768, inter=2048, H=8, Hkuv=8, E=8, B=1, S=8, rmsnorm=False, seed=3, full=False)
     # the 370M model's layer dims (hidden 1024, 8 heads of 128, 11 x 256), per-head RMSNorm on
     run_case(C, M, "layer_370m_dims", hidden=1024, inter=2816, H=8, Hkuv=8, E=11, B=1, S=8, rmsnorm=True, seed=4, full=False)
+    # dot scaling and final scaling on (head/up = sqrt(H), final = sqrt(3/8)), every tensor stored
+    run_case(C, M, "layer_tiny_scaled", hidden=128, inter=128, H=2, Hkuv=2, E=2, B=2, S=20, rmsnorm=True, seed=5, full=True,
+             scaled=True)
+    # the single-layer fp32 configuration in full: batch 2 x 512 tokens, hidden 768, 8 heads of 96, 8 x 256
+    run_case(C, M, "layer_128m_full", hidden=768, inter=2048, H=8, Hkuv=8, E=8, B=2, S=512, rmsnorm=False, seed=6,
+             full=False, big=True)
 
 
 if __name__ == "__main__":

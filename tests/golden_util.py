@@ -11,8 +11,13 @@ def load_golden(name):
     z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
     d = {k: torch.from_numpy(z[k]) for k in z.files}
     hidden, inter, H, Hkuv, E, B, S, rms, seed, skip = (int(v) for v in d.pop("meta"))
+    scaling = tuple(float(v) for v in d.pop("scaling")) if "scaling" in d else (1.0, 1.0, 1.0)
     d["cfg"] = dict(hidden=hidden, inter=inter, H=H, Hkuv=Hkuv, E=E, B=B, S=S, rmsnorm=bool(rms), seed=seed,
-                    skip_linear=bool(skip), dh=hidden // H)
+                    skip_linear=bool(skip), dh=hidden // H, scaling=scaling)
+    if "x" not in d:   # full-size cases: the input and the loss weights are regenerated from the seed
+        g = torch.Generator().manual_seed(seed + 1000)
+        d["x"] = torch.randn(B, S, hidden, generator=g)
+        d["wloss"] = torch.randn(B, S, hidden, generator=g)
     return d
 
 

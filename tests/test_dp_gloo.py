@@ -41,6 +41,17 @@ def _worker(rank, world, port, out):
         errs = [orc.rel_l2(x, y) for x, y in zip((dK, dU, dV), full[1:4])]
         errs.append(orc.rel_l2(O_local, orc.mhffn_forward(Q, K, U, V, R)[a:b]))
         errs.append(orc.rel_l2(dQ, full[0][a:b]))
+        # the same exchange with the weight gradients written into one bucket first and reduced under the dQ/dR half
+        bucket = dp.WeightGradBucket(K)
+
+        def weights_fn(views):
+            for v, g in zip(views, orc.mhffn_backward(Qs, K, U, V, Rs, dO[a:b])[1:4]):
+                v.copy_(g)
+
+        dQ2, dR2 = dp.exchange_under_inputs(weights_fn, lambda: (dQ.clone(), dR.clone()), bucket)
+        errs += [orc.rel_l2(x, y) for x, y in zip(bucket.views, full[1:4])]
+        errs.append(orc.rel_l2(dQ2, full[0][a:b]))
+        assert bucket.views[0].data_ptr() == bucket.flat.data_ptr() and bucket.flat.numel() == 3 * K.numel()
         t = dp.max_over_ranks(10.0 + rank, torch.device("cpu"))
         out.put((rank, (a, b), errs, t))
     finally:

@@ -60,5 +60,32 @@ def test_reference_import_seam_modules_run_on_gpu():
     ref1 = orc.mhffn_forward(Q.cpu().float(), K[:, :1].cpu().float(), U[:, :1].cpu().float(), V[:, :1].cpu().float(),
                              torch.ones(1, 2, 100, 1))
     assert orc.rel_l2(o.cpu().float(), ref1) < 1e-2
-    with pytest.raises(ValueError):
-        FlashMLP()(Q, K[:, 0], U[:, 0], V[:, 0], True, 2.0, 2.0, "silu")
+
+
+def test_unmodified_reference_layer_runs_the_cuda_operator_through_its_import_seam():
+    """Where a checkout of the reference is at hand (never on a bare GPU box: then skipped), build its own
+    MHFFNMoEMultiHeadFFNFlash(cfg, use_flash=True) after install_reference_seam(): its constructor import
+    (modeling_mhffnmoe.py:318-329) must pick up this package's FlashMLPMoE, and its flash branch (:394-408) must give
+    what its eager branch gives."""
+    import os
+    import flashmhf_b200
+    from tests.golden.make_golden import load_reference, seeded_params
+    ref_root = next((p for p in (os.environ.get("FLASHMHF_REFERENCE", ""), "/root/reference",
+                                 os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref"))
+                     if p and os.path.exists(os.path.join(p, "models", "flashmhf", "modeling_mhffnmoe.py"))), None)
+    if ref_root is None:
+        pytest.skip("no reference checkout on this machine")
+    flashmhf_b200.install_reference_seam()
+    C_, M = load_reference(ref_root)
+    cfg = C_.MHFFNMoEConfig(hidden_size=256, intermediate_size=256, num_attention_heads=4, mhffnmoe_num_heads=2,
+                            mhffnmoe_num_kuv_heads=2, mhffnmoe_num_experts=2, mhffnmoe_use_flash=True,
+                            mhffnmoe_custom_init=True, mhffnmoe_apply_rmsnorm=True, rms_norm_eps=1e-5)
+    layer = M.MHFFNMoEMultiHeadFFNFlash(cfg, use_flash=True)
+    assert layer.flash and type(layer.flash_mlp).__module__ == "ops.flash_mlp_moe"
+    seeded_params(layer, 7)
+    layer = layer.cuda().to(torch.bfloat16)
+    x = torch.randn(2, 150, 256, generator=torch.Generator().manual_seed(8)).cuda().to(torch.bfloat16)
+    y_flash = layer(x)
+    layer.flash = False
+    y_eager = layer(x)
+    assert orc.rel_l2(y_flash.float().cpu(), y_eager.float().cpu()) < 2e-2

@@ -6,7 +6,9 @@ FFI and have no device allocator to pass in (and cudaMalloc/cudaFree would stall
 anyway).  For them the library keeps the dK/dU/dV partial sums in a 72 MiB static device array.  This
 test calls that entry point through the C ABI, twice in a row on different inputs (the second,
 smaller problem runs over the first call's leftovers in the shared array), and checks each result
-against the ordinary flashmhf_backward on the same inputs, at the tolerance of the bf16 parity tests.
+against the ordinary flashmhf_backward on the same inputs: both run the same deterministic kernels,
+so the results must be equal bit for bit.  It also checks what the entry point is for: across a call
+neither the device's free memory nor torch's allocator moves.
 
 Collected last (file name) so that a run stopping at the first failure has already run every other test.
 """
@@ -18,23 +20,30 @@ import torch
 from oracle import mhffn_oracle as orc
 
 pytestmark = pytest.mark.gpu
-TOL_BF16 = 1e-2
 
 
-def _static_backward(Q, K, U, V, R, dO):
+def _static_backward(Q, K, U, V, R, dO, outs=None):
     """The test is the caller: it owns inputs and outputs; the library call itself allocates nothing."""
     from flashmhf_b200 import _lib
     from flashmhf_b200.functional import _dims, _tensor
     lib = _lib.load()
     B, H, S, dh = Q.shape
     hk, E, de, _ = K.shape
-    outs = [torch.full_like(t, float("nan")) for t in (Q, K, U, V)] + [torch.full_like(R, float("nan"))]
+    if outs is None:
+        outs = [torch.full_like(t, float("nan")) for t in (Q, K, U, V)] + [torch.full_like(R, float("nan"))]
     p = _lib.BwdParams(_dims(B, H, S, dh, hk, E, de, Q.dtype), _tensor(Q), _tensor(K), _tensor(U), _tensor(V),
-                       _tensor(R), _tensor(dO), *[_tensor(t) for t in outs], None, 0)   # no workspace passed
-    _lib.check(lib.flashmhf_backward_static_scratch(C.byref(p), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+                       _tensor(R), _tensor(dO), *[_tensor(t) for t in outs], None, 0,   # no workspace passed
+                       _lib.Scaling(1.0, 1.0, 1.0), 0)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
+    free0, alloc0, reserved0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    rc = lib.flashmhf_backward_static_scratch(C.byref(p), stream)
+    torch.cuda.synchronize()
+    moved = (torch.cuda.mem_get_info()[0] - free0, torch.cuda.memory_allocated() - alloc0,
+             torch.cuda.memory_reserved() - reserved0)
+    _lib.check(rc)
     _lib.device_status()
-    return outs
+    return outs, moved
 
 
 def test_static_scratch_matches_workspace_entry_point_two_calls_in_a_row():
@@ -47,10 +56,15 @@ def test_static_scratch_matches_workspace_entry_point_two_calls_in_a_row():
         d = _lib.Dims(B, H, S, dh, Hk, E, de, _lib.BF16)
         assert 0 < _lib.load().flashmhf_backward_workspace_bytes(C.byref(d)) <= _lib.STATIC_SCRATCH_BYTES
         want = fm.backward_raw(*ins)
-        got = _static_backward(*ins)
+        got, _ = _static_backward(*ins)            # on a device's first call this also looks up the array's address
         for name, a, b in zip("dQ dK dU dV dR".split(), got, want):
             assert torch.isfinite(a.float()).all(), name
-            assert orc.rel_l2(a.float().cpu(), b.float().cpu()) < TOL_BF16, (i, name)
+            assert torch.equal(a, b), (i, name)
+        # once more into the same output buffers: the call must leave the device's memory exactly as it found it
+        again, moved = _static_backward(*ins, outs=got)
+        assert moved == (0, 0, 0), f"free / allocated / reserved bytes moved by {moved}"
+        for name, a, b in zip("dQ dK dU dV dR".split(), again, want):
+            assert torch.equal(a, b), (i, name)
 
 
 def test_static_scratch_refuses_oversized_and_check_mode():
@@ -62,7 +76,7 @@ def test_static_scratch_refuses_oversized_and_check_mode():
     assert lib.flashmhf_backward_workspace_bytes(C.byref(d)) > _lib.STATIC_SCRATCH_BYTES
     x = torch.zeros(16, device="cuda", dtype=torch.bfloat16)   # never read: the size check comes first
     t = _tensor(x.view(1, 1, 1, 16))
-    p = _lib.BwdParams(d, *[t] * 11, None, 0)
+    p = _lib.BwdParams(d, *[t] * 11, None, 0, _lib.Scaling(1.0, 1.0, 1.0), 0)
     assert lib.flashmhf_backward_static_scratch(C.byref(p), None) == -10
     assert b"72 MiB" in lib.flashmhf_strerror(-10)
     p.d.dtype = _lib.F32_CHECK
