@@ -6,7 +6,7 @@ import os
 import threading
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "lib", "libflashmhf_b200.so")
+LIB_PATH = os.environ.get("FLASHMHF_LIB") or os.path.join(_PKG, "lib", "libflashmhf_b200.so")   # FLASHMHF_LIB: another build of the same ABI
 ABI_VERSION = 3
 
 BF16, F32_CHECK = 0, 1

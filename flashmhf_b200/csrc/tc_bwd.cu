@@ -33,7 +33,15 @@
 namespace fmhf {
 namespace {
 
-constexpr int kBT = 128, kBI = 64, kThreads = 384, kActThreads = 256;
+#ifndef FMHF_BWD_PARTS
+#define FMHF_BWD_PARTS 2
+#endif
+// Element-wise warps: 4 lane quarters x kParts column parts of a 64-column block (a thread = one token row x
+// kCols columns).  More, narrower threads shorten the arithmetic phase of a block; the fixed part of a block's
+// element-wise step (barrier waits, tensor-memory load and store latencies) does not shrink.
+constexpr int kParts = FMHF_BWD_PARTS, kCols = 64 / kParts, kSubs = kCols / 16;
+constexpr int kBT = 128, kBI = 64, kActThreads = 128 * kParts, kThreads = 128 + kActThreads;
+constexpr int kEpiThreads = 256;  // the warps of column parts 0 and 1 write the accumulators out
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTile = kBT * 128;    // one 128-row x 64-col SW128 chunk: 16 KB
 constexpr uint32_t kWChunk = kBI * 128;  // one 64-row x 64-col chunk: 8 KB
@@ -79,14 +87,12 @@ struct DqSmem {
     static constexpr uint32_t kKUStage = kChunks * 2 * kWChunk;  // per chunk: [K;U] = 128 rows
     static constexpr uint32_t kVStage = kChunks * kWChunk;
     static constexpr int kKUStages = 3, kVStages = 2;
-    static constexpr uint32_t kPBytes = 2 * kTile;  // [dM | dN]
     static constexpr uint32_t kOffQ = 0;
     static constexpr uint32_t kOffdO = kOffQ + kQBytes;
     static constexpr uint32_t kOffKU = kOffdO + kQBytes;
     static constexpr uint32_t kOffV = kOffKU + kKUStages * kKUStage;
-    static constexpr uint32_t kOffP = kOffV + kVStages * kVStage;
-    static constexpr uint32_t kOffCtl = kOffP + kPBytes;
-    static constexpr uint32_t kCtlBytes = 256 + 2 * 128 * 4;  // barriers + two dR exchange rows
+    static constexpr uint32_t kOffCtl = kOffV + kVStages * kVStage;
+    static constexpr uint32_t kCtlBytes = 256 + 2 * (kParts - 1) * 128 * 4;  // barriers + two sets of dR exchange rows
     static constexpr uint32_t kTotal = kOffCtl + kCtlBytes + 1024;
 };
 
@@ -114,7 +120,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *gbase = smem_raw + (base - raw);
     const uint32_t sQ = base + L::kOffQ, sdO = base + L::kOffdO, sKU = base + L::kOffKU, sV = base + L::kOffV,
-                   sP = base + L::kOffP, sBar = base + L::kOffCtl;
+                   sBar = base + L::kOffCtl;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gbase + L::kOffCtl + DQ_BARS * 8);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(gbase + L::kOffCtl + DQ_BARS * 8 + 4);
     volatile float *drx = reinterpret_cast<volatile float *>(gbase + L::kOffCtl + 256);  // [2][128]
@@ -137,8 +143,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             mbar_init(bar(DQ_SEMPTY + i), arrivals_of(kActThreads));  // S and dA of the buffer are in registers
             mbar_init(bar(DQ_PFULL + i), arrivals_of(kActThreads));   // [dM|dN] written over the dA columns
             mbar_init(bar(DQ_DAFREE + i), 1);            // the dQ update that read [dM|dN] is done
-            mbar_init(bar(DQ_DRFULL + i), arrivals_of(kActThreads / 2));  // the upper column half has written its dR_e partial
-            mbar_init(bar(DQ_DRFREE + i), arrivals_of(kActThreads / 2));  // the lower half has read it: the row may be reused
+            mbar_init(bar(DQ_DRFULL + i), arrivals_of(kActThreads - 128));  // column parts 1.. have written their dR_e partials
+            mbar_init(bar(DQ_DRFREE + i), arrivals_of(128));                 // part 0 has read them: the rows may be reused
         }
         mbar_init(bar(DQ_ACCFULL), 1);
         fence_mbar_init();
@@ -256,15 +262,16 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                 tc_fence_after();
                 const uint64_t dku = dKUmn0 + sk * kKUStep;
                 const uint32_t tP = tmem + kColS0 + bb * kBufStride + kColdA;
-                // [dM|dN] sits over the 64 dA columns as packed bf16 pairs.  The thread that handled columns
-                // [32h, 32h+32) of the block wrote its dM to dA columns [32h, 32h+16) and its dN to
-                // [32h+16, 32h+32) -- columns only it had read.  K step k (16 values = 8 columns; steps 0-3
-                // pair with the K rows of the stage, 4-7 with the U rows) is at
-                // ((k%4)/2)*32 + (k/4)*16 + (k%2)*8.
+                // [dM|dN] sits over the 64 dA columns as packed bf16 pairs.  The thread that handled block columns
+                // [c, c + kCols) wrote its dM to dA columns [c, c + kCols/2) and its dN to [c + kCols/2, c + kCols) --
+                // columns only it had read.  K step k (16 values = 8 columns; steps 0-3 pair with the K rows of the
+                // stage, 4-7 with the U rows) covers block columns [16 (k%4), 16 (k%4) + 16).
 #pragma unroll
-                for (int k = 0; k < 8; ++k)
-                    umma_ts(tmem + kColAcc, tP + ((k & 3) >> 1) * 32 + (k >> 2) * 16 + (k & 1) * 8, dku + k * 128, idQ,
-                            (j > 0 || k > 0) ? 1u : 0u);
+                for (int k = 0; k < 8; ++k) {
+                    const int bc = 16 * (k & 3);
+                    const int col = (bc / kCols) * kCols + (bc % kCols) / 2 + (k >> 2) * (kCols / 2);
+                    umma_ts(tmem + kColAcc, tP + col, dku + k * 128, idQ, (j > 0 || k > 0) ? 1u : 0u);
+                }
                 umma_commit(bar(DQ_KUEMPTY + sk));
                 umma_commit(bar(DQ_DAFREE + bb));
                 if (++sk == L::kKUStages) sk = 0;
@@ -272,7 +279,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             if (ok) umma_commit(bar(DQ_ACCFULL));
         }
     } else if (warp >= 4) {
-        const int quarter = warp & 3, half = (warp - 4) >> 2;
+        const int quarter = warp & 3, part = (warp - 4) >> 2, half = part;  // part: which kCols of the block's 64 columns
         const int row = quarter * 32 + lane, t = t0 + row;
         const bool in_range = t < args.S;
         const float *rrow = args.R + (long long)b * args.r_sb + (long long)h * args.r_sh + (long long)t * args.r_ss;
@@ -292,14 +299,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
             if (!mbar_wait(bar(DQ_SFULL + bb), nb & 1, ctl, W + 7)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t tS = lane_base + kColS0 + bb * kBufStride + half * 32;
-            uint32_t pm[16], pn[16];  // packed bf16 pairs of dM, dN for this thread's 32 columns
+            const uint32_t tS = lane_base + kColS0 + bb * kBufStride + part * kCols;
+            uint32_t pm[kCols / 2], pn[kCols / 2];  // packed bf16 pairs of dM, dN for this thread's columns
             const f32x2 r2 = f2_pack(args.c * r_cur, args.c * r_cur);
 #pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {
+            for (int sub = 0; sub < kSubs; ++sub) {
                 uint32_t m[16], n[16], da[16];
                 tmem_ld16x3_sync(tS + sub * 16, tS + kBI + sub * 16, tS + kColdA + sub * 16, m, n, da);
-                if (sub == 1) {   // S is in registers: it may be recomputed for block j+2 from here on
+                if (sub == kSubs - 1) {   // S is in registers: it may be recomputed for block j+2 from here on
                     tc_fence_before();
                     warp_arrive(bar(DQ_SEMPTY + bb));
                 }
@@ -312,33 +319,42 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                     pn[sub * 8 + i] = f2_to_bf16x2(x.dn);
                 }
             }
-            // dM and dN go back into tensor memory as packed bf16 pairs, over the 32 dA columns this
-            // thread has just read (no other thread reads those columns)
-            tmem_st16(tS + kColdA, pm);
-            tmem_st16(tS + kColdA + 16, pn);
+            // dM and dN go back into tensor memory as packed bf16 pairs, over the dA columns this thread has just
+            // read (no other thread reads those columns)
+            if (kCols == 32) {
+                tmem_st16(tS + kColdA, pm);
+                tmem_st16(tS + kColdA + 16, pn);
+            } else {
+                tmem_st8(tS + kColdA, pm);
+                tmem_st8(tS + kColdA + 8, pn);
+            }
             tmem_st_wait();
             tc_fence_before();
             warp_arrive(bar(DQ_PFULL + bb));
-            if (++in_e == bpe) {  // sub-network finished: add the two column halves of dR_e
+            if (++in_e == bpe) {  // sub-network finished: add the column parts of dR_e, in part order
                 const int xb = e & 1;
                 float dr_lo, dr_hi;
                 f2_unpack(dr2, dr_lo, dr_hi);
                 const float dr_acc = (dr_lo + dr_hi) * args.c;
-                if (half == 1) {
-                    // the exchange row of sub-network e was last used by e - 2: wait until that value has been read
+                volatile float *xrow = drx + (xb * (kParts - 1)) * 128 + row;
+                if (part != 0) {
+                    // the exchange rows of sub-network e were last used by e - 2: wait until those values have been read
                     if (e >= 2 && !mbar_wait(bar(DQ_DRFREE + xb), ((e >> 1) - 1) & 1, ctl, W + 11)) { ok = false; break; }
-                    drx[xb * 128 + row] = dr_acc;
+                    xrow[(part - 1) * 128] = dr_acc;
                     warp_arrive(bar(DQ_DRFULL + xb));
                 } else {
                     if (!mbar_wait(bar(DQ_DRFULL + xb), (e >> 1) & 1, ctl, W + 9)) { ok = false; break; }
-                    const float other = drx[xb * 128 + row];
+                    float sum = dr_acc;
+#pragma unroll
+                    for (int q = 0; q < kParts - 1; ++q) sum += xrow[q * 128];
                     warp_arrive(bar(DQ_DRFREE + xb));
-                    if (in_range) drrow[e] = dr_acc + other;
+                    if (in_range) drrow[e] = sum;
                 }
                 in_e = 0;
                 ++e;
             }
         }
+        if (part >= 2) ok = false;  // the accumulator is written out by the warps of parts 0 and 1
         if (ok) ok = mbar_wait(bar(DQ_ACCFULL), 0, ctl, W + 10);
         if (ok) {
             tc_fence_after();
@@ -361,7 +377,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             tc_fence_before();
             fence_async_smem();
         }
-        named_bar_sync(1, kActThreads);
+        if (part < 2) named_bar_sync(1, kEpiThreads);
         if (ok && warp == 4 && lane == 0 && !*abort_flag) {
             for (int c = 0; c < L::kChunks; ++c) tma_store_4d(&tmdQ, sQ + c * kTile, c * 64, t0, h, b);
             tma_store_commit();
@@ -592,43 +608,48 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             if (ok) umma_commit(bar(DW_ACCFULL));
         }
     } else if (warp >= 4) {
-        const int quarter = warp & 3, half = (warp - 4) >> 2;
+        const int quarter = warp & 3, part = (warp - 4) >> 2, half = part;  // part: which kCols of the block's 64 columns
         const int row = quarter * 32 + lane;
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
         bool ok = true;
         const BwdConst kc = bwd_const(args.s0);
-        float r_next;
-        {
-            int ts, hh, bb;
-            tile_coords(0, ts, hh, bb);
-            const int t = ts * kBT + row;
-            r_next = (t < args.S) ? __ldg(args.R + (long long)bb * args.r_sb + (long long)hh * args.r_sh +
-                                          (long long)t * args.r_ss + e) : 0.f;
-        }
+        // This row's routing weight for sub-network e, fetched one tile ahead.  The tile's (sequence tile, head, batch)
+        // coordinates advance by counting, with no division in the loop.
+        int c_ts, c_hh, c_bb;
+        tile_coords(0, c_ts, c_hh, c_bb);
+        int c_g = c_hh - hk * args.G;
+        auto r_of_tile = [&]() {
+            const int t = c_ts * kBT + row;
+            return (t < args.S) ? __ldg(args.R + (long long)c_bb * args.r_sb + (long long)(hk * args.G + c_g) * args.r_sh +
+                                        (long long)t * args.r_ss + e) : 0.f;
+        };
+        float r_next = r_of_tile();
         for (int i = 0; i < ntiles; ++i) {
             const float r = r_next;
             if (i + 1 < ntiles) {
-                int ts, hh, bb;
-                tile_coords(i + 1, ts, hh, bb);
-                const int t = ts * kBT + row;
-                r_next = (t < args.S) ? __ldg(args.R + (long long)bb * args.r_sb + (long long)hh * args.r_sh +
-                                              (long long)t * args.r_ss + e) : 0.f;
+                if (++c_ts == args.tiles_per_seq) {
+                    c_ts = 0;
+                    if (++c_g == args.G) { c_g = 0; ++c_bb; }
+                }
+                r_next = r_of_tile();
             }
             const int sb = i % kSB;
             if (!mbar_wait(bar(DW_SFULL + sb), (uint32_t)(i / kSB) & 1u, ctl, W + 7)) { ok = false; break; }
             tc_fence_after();
-            uint32_t pm[16], pn[16], pa[16], da[32];
-            tmem_ld32_sync(lane_base + kColdA + half * 32, da);   // dA first: its single buffer goes straight back
+            uint32_t pm[kCols / 2], pn[kCols / 2], pa[kCols / 2], da[kCols];
+            // dA first: its single buffer goes straight back
+            if (kCols == 32) tmem_ld32_sync(lane_base + kColdA + part * kCols, da);
+            else tmem_ld16_sync(lane_base + kColdA + part * kCols, da);
             tc_fence_before();
             warp_arrive(bar(DW_DAEMPTY));
             const f32x2 r2 = f2_pack(args.c * r, args.c * r);
             const uint32_t colS = kColS + sb * 2 * kBI;
 #pragma unroll
-            for (int sub = 0; sub < 2; ++sub) {
+            for (int sub = 0; sub < kSubs; ++sub) {
                 uint32_t m[16], n[16];
-                const uint32_t c = half * 32 + sub * 16;
+                const uint32_t c = part * kCols + sub * 16;
                 tmem_ld16x2_sync(lane_base + colS + c, lane_base + colS + kBI + c, m, n);
-                if (sub == 1) {   // S is in registers: the buffer can take the tile after next
+                if (sub == kSubs - 1) {   // S is in registers: the buffer can take the tile after next
                     tc_fence_before();
                     warp_arrive(bar(DW_SEMPTY + sb));
                 }
@@ -643,8 +664,8 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
             if (!mbar_wait(bar(DW_PEMPTY), (i & 1) ^ 1, ctl, W + 8)) { ok = false; break; }
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const uint32_t off = sw128_offset(row, half * 4 + q);
+            for (int q = 0; q < kCols / 8; ++q) {
+                const uint32_t off = sw128_offset(row, part * (kCols / 8) + q);
                 st_shared_v4(sP + off, pm[4 * q], pm[4 * q + 1], pm[4 * q + 2], pm[4 * q + 3]);
                 st_shared_v4(sP + kTile + off, pn[4 * q], pn[4 * q + 1], pn[4 * q + 2], pn[4 * q + 3]);
             }
@@ -652,11 +673,12 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             warp_arrive(bar(DW_PFULL));
             if (!mbar_wait(bar(DW_AEMPTY), (i & 1) ^ 1, ctl, W + 8)) { ok = false; break; }
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-                st_shared_v4(sA + sw128_offset(row, half * 4 + q), pa[4 * q], pa[4 * q + 1], pa[4 * q + 2], pa[4 * q + 3]);
+            for (int q = 0; q < kCols / 8; ++q)
+                st_shared_v4(sA + sw128_offset(row, part * (kCols / 8) + q), pa[4 * q], pa[4 * q + 1], pa[4 * q + 2], pa[4 * q + 3]);
             fence_async_smem();
             warp_arrive(bar(DW_AFULL));
         }
+        if (part >= 2) ok = false;  // the accumulators are written out by the warps of parts 0 and 1
         if (ok) ok = mbar_wait(bar(DW_ACCFULL), 0, ctl, W + 9);
         if (ok) {
             tc_fence_after();

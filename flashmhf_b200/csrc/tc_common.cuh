@@ -190,6 +190,11 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// Register reallocation between warpgroups (whole warpgroups of 4 warps execute these together): the control warps give
+// registers back, the element-wise warps take them.  `N` is a multiple of 8.
+template <int N> __device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+
 // ------------------------------------------------------------------------------------ tensor memory
 // Whole-warp operations.  `slot` is a shared-memory word that receives the base address.
 __device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t ncols) {
@@ -228,6 +233,17 @@ __device__ __forceinline__ void tmem_ld32x2_sync(uint32_t ta, uint32_t tb, uint3
           "=r"(b[8]), "=r"(b[9]), "=r"(b[10]), "=r"(b[11]), "=r"(b[12]), "=r"(b[13]), "=r"(b[14]), "=r"(b[15]),
           "=r"(b[16]), "=r"(b[17]), "=r"(b[18]), "=r"(b[19]), "=r"(b[20]), "=r"(b[21]), "=r"(b[22]), "=r"(b[23]),
           "=r"(b[24]), "=r"(b[25]), "=r"(b[26]), "=r"(b[27]), "=r"(b[28]), "=r"(b[29]), "=r"(b[30]), "=r"(b[31])
+        : "r"(ta), "r"(tb)
+        : "memory");
+}
+// 64 + 64 consecutive fp32 columns (e.g. a thread's whole row of M and of N of a 64-column block) in one statement.
+__device__ __forceinline__ void tmem_ld64x2_sync(uint32_t ta, uint32_t tb, uint32_t *a, uint32_t *b) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%128];\n\t"
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%64,%65,%66,%67,%68,%69,%70,%71,%72,%73,%74,%75,%76,%77,%78,%79,%80,%81,%82,%83,%84,%85,%86,%87,%88,%89,%90,%91,%92,%93,%94,%95,%96,%97,%98,%99,%100,%101,%102,%103,%104,%105,%106,%107,%108,%109,%110,%111,%112,%113,%114,%115,%116,%117,%118,%119,%120,%121,%122,%123,%124,%125,%126,%127}, [%129];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3]), "=r"(a[4]), "=r"(a[5]), "=r"(a[6]), "=r"(a[7]), "=r"(a[8]), "=r"(a[9]), "=r"(a[10]), "=r"(a[11]), "=r"(a[12]), "=r"(a[13]), "=r"(a[14]), "=r"(a[15]), "=r"(a[16]), "=r"(a[17]), "=r"(a[18]), "=r"(a[19]), "=r"(a[20]), "=r"(a[21]), "=r"(a[22]), "=r"(a[23]), "=r"(a[24]), "=r"(a[25]), "=r"(a[26]), "=r"(a[27]), "=r"(a[28]), "=r"(a[29]), "=r"(a[30]), "=r"(a[31]), "=r"(a[32]), "=r"(a[33]), "=r"(a[34]), "=r"(a[35]), "=r"(a[36]), "=r"(a[37]), "=r"(a[38]), "=r"(a[39]), "=r"(a[40]), "=r"(a[41]), "=r"(a[42]), "=r"(a[43]), "=r"(a[44]), "=r"(a[45]), "=r"(a[46]), "=r"(a[47]), "=r"(a[48]), "=r"(a[49]), "=r"(a[50]), "=r"(a[51]), "=r"(a[52]), "=r"(a[53]), "=r"(a[54]), "=r"(a[55]), "=r"(a[56]), "=r"(a[57]), "=r"(a[58]), "=r"(a[59]), "=r"(a[60]), "=r"(a[61]), "=r"(a[62]), "=r"(a[63]),
+          "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]), "=r"(b[4]), "=r"(b[5]), "=r"(b[6]), "=r"(b[7]), "=r"(b[8]), "=r"(b[9]), "=r"(b[10]), "=r"(b[11]), "=r"(b[12]), "=r"(b[13]), "=r"(b[14]), "=r"(b[15]), "=r"(b[16]), "=r"(b[17]), "=r"(b[18]), "=r"(b[19]), "=r"(b[20]), "=r"(b[21]), "=r"(b[22]), "=r"(b[23]), "=r"(b[24]), "=r"(b[25]), "=r"(b[26]), "=r"(b[27]), "=r"(b[28]), "=r"(b[29]), "=r"(b[30]), "=r"(b[31]), "=r"(b[32]), "=r"(b[33]), "=r"(b[34]), "=r"(b[35]), "=r"(b[36]), "=r"(b[37]), "=r"(b[38]), "=r"(b[39]), "=r"(b[40]), "=r"(b[41]), "=r"(b[42]), "=r"(b[43]), "=r"(b[44]), "=r"(b[45]), "=r"(b[46]), "=r"(b[47]), "=r"(b[48]), "=r"(b[49]), "=r"(b[50]), "=r"(b[51]), "=r"(b[52]), "=r"(b[53]), "=r"(b[54]), "=r"(b[55]), "=r"(b[56]), "=r"(b[57]), "=r"(b[58]), "=r"(b[59]), "=r"(b[60]), "=r"(b[61]), "=r"(b[62]), "=r"(b[63])
         : "r"(ta), "r"(tb)
         : "memory");
 }
@@ -344,9 +360,23 @@ __device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
     return d;
 }
 __device__ __forceinline__ f32x2 f2_tanh(f32x2 v) {
+#if defined(FMHF_EXP_NOTANH)
+    return v;
+#elif defined(FMHF_EXP_TANH_H2)
+    // one MUFU op for both values: f16x2 tanh (11-bit mantissa, the accuracy class of tanh.approx.f32)
+    float a, b;
+    f2_unpack(v, a, b);
+    uint32_t h, t;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(b), "f"(a));
+    asm("tanh.approx.f16x2 %0, %1;" : "=r"(t) : "r"(h));
+    float ta, tb;
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}" : "=f"(ta), "=f"(tb) : "r"(t));
+    return f2_pack(ta, tb);
+#else
     float a, b;
     f2_unpack(v, a, b);
     return f2_pack(fast_tanh(a), fast_tanh(b));
+#endif
 }
 __device__ __forceinline__ uint32_t f2_to_bf16x2(f32x2 v) {
     float a, b;

@@ -4,25 +4,30 @@
 // weights of the head stream through shared-memory rings, 64 intermediate rows (one "block": 64
 // rows of K_e, U_e and V_e) at a time.  Per block the tensor core computes
 //     S = Q [K_blk; U_blk]^T      (128 x 128, one MMA chain, fp32 in tensor memory: M | N)
-// an activation warpgroup reads S, forms A = bf16(SiLU(M) * N * R_e) in registers and writes it
-// back into tensor memory over the first 32 columns of the same S buffer (two bf16 per column), and
-// the tensor core accumulates, with A read from tensor memory and V from shared memory,
+// the activation warps read S, form A = bf16(SiLU(M) * N * R_e) in registers and write it back into
+// tensor memory (two bf16 per column), and the tensor core accumulates, with A read from tensor memory
+// and V from shared memory,
 //     O += A V_blk                (128 x d_h, fp32 in tensor memory, over all blocks of all e)
 // so the [T, E*d_e] intermediate never leaves the SM and A never touches shared memory.
 //
 // Pipeline.  The hand-off from an MMA to the warps that consume its result costs several hundred
 // cycles (commit -> mbarrier -> wake-up) and the tensor pipe accepts MMAs only a few ahead of their
-// execution, so (a) three S buffers keep three blocks in flight, (b) the two MMA chains are issued
-// by two different threads -- one runs ahead with S = Q [K;U]^T, the other follows with O += A V --
-// so that neither waits on the other's barriers, and (c) the two activation warpgroups own
-// alternate blocks (even / odd), so the load/store phases of one overlap the arithmetic of the other.
+// execution, so nothing on the S path waits for anything on the O path:
+//   * Q is copied once from shared into tensor memory and the S chain reads it from there: an MMA with both
+//     operands in shared memory uses the whole shared-memory bandwidth of the SM (measured: 128x128x16 takes
+//     64.5 clk = 8 KB at 128 B/clk), which the weight tiles arriving by TMA need as well.
+//   * S has two buffers.  A thread's first step on a block is to load its part of M and N into registers,
+//     after which the buffer is free again -- S of block j+2 may be issued while block j is still being activated.
+//   * A has slots of its own (32 columns each), so the O update of a block may lag its activation without
+//     holding an S buffer.
+//   * The two MMA chains are issued by different threads (S by two threads, one per S buffer, so that each
+//     sees every phase of the barriers of its buffer; O by a third).
 //
-// Warp roles (384 threads): warp 0 TMA producer, warps 1-2 MMA issuers for S (even / odd blocks;
-// warp 1 owns tensor memory), warp 3 MMA issuer for O, warps 4-7 activation warpgroup 0,
-// warps 8-11 activation warpgroup 1 (warp % 4 = TMEM lane quarter = 32 token rows; one thread = one
-// token row of a block).
+// Warp roles: warp 0 TMA producer, warps 1-2 MMA issuers for S (even / odd blocks; warp 1 owns tensor
+// memory), warp 3 MMA issuer for O, then the activation warps (warp % 4 = TMEM lane quarter = 32 token rows).
 //
-// Tensor memory (512 columns): O at [0, d_h), S buffers at [128, 256), [256, 384), [384, 512).
+// Tensor memory (512 columns): O at [0, d_h), Q (bf16) at [128, 192), A slots at [192, 256), S buffers at
+// [256, 384), [384, 512).
 #include <atomic>
 
 #include "kernels.h"
@@ -34,12 +39,18 @@ namespace {
 
 constexpr int kBT = 128;  // token rows per tile
 constexpr int kBI = 64;   // intermediate rows per block
-constexpr int kDepth = 3; // S buffers in tensor memory = blocks in flight
-constexpr int kRing = 4;  // shared-memory stages of the [K;U] ring and of the V ring
-constexpr int kThreads = 384;
-constexpr int kGroupThreads = 128;  // one activation warpgroup
+constexpr int kSBufs = 2;   // S buffers in tensor memory
+constexpr int kRing = 4;    // shared-memory stages of the [K;U] ring and of the V ring
+// Activation teams of eight warps (warp % 4 = lane quarter, next bit = which 32 of a block's 64 columns).  With two
+// teams, team t owns the blocks j = t (mod 2) and with them S buffer t and A slot t; the two teams are then in
+// different phases of their loop (wait, load, arithmetic, store), which keeps the arithmetic pipes busy.
+// One team at d_h = 128, where the kernel is paced by the arrival of the weight tiles from L2 (48 KB per block at
+// about 50 B/clk per SM) and by the tensor pipe; two teams at d_h = 64 and 96, where it is paced by the activation.
+constexpr int kTeamThreads = 256;
+__host__ __device__ constexpr int teams_for(int dh) { return dh == 128 ? 1 : 2; }
+__host__ __device__ constexpr int threads_for(int dh) { return 128 + teams_for(dh) * kTeamThreads; }
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColO = 0, kColS0 = 128, kColSStride = 128;
+constexpr uint32_t kColO = 0, kColQ = 128, kColA0 = 192, kColAStride = 32, kColS0 = 256, kColSStride = 128;
 
 template <int DH>
 struct FwdSmem {
@@ -57,15 +68,12 @@ struct FwdSmem {
 };
 
 // barrier slots (8 bytes each) inside the control area
-// SFULL: S computed; AFULL: A written over it; SFREE: O += A V done, buffer reusable
-// The three S-buffer barriers exist in 2 * kDepth copies, indexed by block % (2 * kDepth).  Blocks of
-// even and odd index are handled by different threads (two S issuers, two activation warpgroups), so
-// with one barrier per buffer a waiter would see only every other phase of it, and a one-bit phase
-// parity cannot tell "two phases behind" from "done".  With 2 * kDepth barriers every barrier has one
-// fixed waiter that observes each of its phases.
-enum { BAR_Q = 0, BAR_KUFULL = 1, BAR_KUEMPTY = 5, BAR_VFULL = 9, BAR_VEMPTY = 13, BAR_SFULL = 17, BAR_AFULL = 23,
-       BAR_SFREE = 29, BAR_OFULL = 35, BAR_COUNT = 36 };
-constexpr int kSBars = 2 * kDepth;
+// SFULL[b]: S computed into buffer b; SEMPTY[b]: every warp of the team working on it has its part in registers;
+// AFULL[s]: A written to slot s; AFREE[s]: the O update that read slot s is done; QT: Q copied to tensor memory.
+// Buffer and slot of block j are j % 2, so every barrier is used once every two blocks and each has one fixed set
+// of waiters that observes each of its phases: a one-bit phase parity is enough.
+enum { BAR_Q = 0, BAR_KUFULL = 1, BAR_KUEMPTY = 5, BAR_VFULL = 9, BAR_VEMPTY = 13, BAR_SFULL = 17, BAR_SEMPTY = 19,
+       BAR_AFULL = 21, BAR_AFREE = 23, BAR_OFULL = 25, BAR_QT = 26, BAR_COUNT = 27 };
 
 struct FwdArgs {
     const float *R;
@@ -93,11 +101,12 @@ struct RingPos {
 };
 
 template <int DH>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(threads_for(DH), 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
            const __grid_constant__ CUtensorMap tmU, const __grid_constant__ CUtensorMap tmV,
            const __grid_constant__ CUtensorMap tmO, const FwdArgs args) {
     using L = FwdSmem<DH>;
+    constexpr int kTeams = teams_for(DH);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -125,12 +134,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             mbar_init(bar(BAR_VFULL + i), 1);
             mbar_init(bar(BAR_VEMPTY + i), 1);
         }
-        for (int i = 0; i < kSBars; ++i) {
+        for (int i = 0; i < kSBufs; ++i) {
             mbar_init(bar(BAR_SFULL + i), 1);
-            mbar_init(bar(BAR_AFULL + i), arrivals_of(kGroupThreads));
-            mbar_init(bar(BAR_SFREE + i), 1);
+            mbar_init(bar(BAR_SEMPTY + i), arrivals_of(kTeamThreads));
+            mbar_init(bar(BAR_AFULL + i), arrivals_of(kTeamThreads));
+            mbar_init(bar(BAR_AFREE + i), 1);
         }
         mbar_init(bar(BAR_OFULL), 1);
+        mbar_init(bar(BAR_QT), arrivals_of(kTeamThreads));
         fence_mbar_init();
     }
     if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
@@ -180,72 +191,63 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         }
     } else if (warp == 1 || warp == 2) {
         // ------------------------------------------------------------------ MMA issuers for S = Q [K;U]^T
-        // Two threads (warp 1: even blocks, warp 2: odd blocks): while one is between batches -- barrier
-        // polls, commits -- the other keeps the tensor pipe fed.  Blocks are independent (own S buffer).
-        // One thread issues the chain, so its instruction stream is kept minimal: descriptors are built
-        // once and advanced by adding constants (the address field counts 16-byte units).
+        // Two threads (warp 1: even blocks into S buffer 0, warp 2: odd blocks into buffer 1): while one is between
+        // batches -- barrier polls, commits -- the other keeps the tensor pipe fed.  Q is read from tensor memory.
+        // One thread issues a chain, so its instruction stream is kept minimal: descriptors are built once and
+        // advanced by adding constants (the address field counts 16-byte units).
         if (lane == 0) {
             constexpr uint32_t idesc1 = umma_idesc(128, 2 * kBI, false, false);
-            const uint64_t dQ = desc_kmajor(sQ), dKU0 = desc_kmajor(sKU);
+            const uint64_t dKU0 = desc_kmajor(sKU);
             constexpr uint64_t kKUStep = L::kKUStage >> 4;
-            const int first = warp - 1;
-            bool ok = mbar_wait(bar(BAR_Q), 0, ctl, W + 3);
+            const int sb = warp - 1;
+            const uint32_t tS = tmem + kColS0 + sb * kColSStride, tQ = tmem + kColQ;
+            bool ok = mbar_wait(bar(BAR_QT), 0, ctl, W + 3);
             RingPos<kRing> pw;   // [K;U] stage of block j
-            RingPos<kSBars> ps;  // barrier set of block j; its S buffer is ps.slot % kDepth
-            RingPos<kSBars> pf;  // barrier set of block j - kDepth, the previous user of that buffer
-            pf.lap = 1;          // so that the lap parity is 0 once j - kDepth reaches 0
-            pw.advance(first);
-            ps.advance(first);
-            pf.advance(first + kDepth);
-            for (int j = first; ok && j < nblk; j += 2) {
+            pw.advance(sb);
+            for (int j = sb; ok && j < nblk; j += 2) {
                 if (!mbar_wait(bar(BAR_KUFULL + pw.slot), pw.lap, ctl, W + 4)) break;
-                if (j >= kDepth && !mbar_wait(bar(BAR_SFREE + pf.slot), pf.lap, ctl, W + 5)) break;
+                // the buffer's previous block (j - 2) is in the activation warps' registers
+                if (j >= 2 && !mbar_wait(bar(BAR_SEMPTY + sb), ((j >> 1) - 1) & 1, ctl, W + 5)) break;
                 tc_fence_after();
                 const uint64_t dku = dKU0 + pw.slot * kKUStep;
-                const uint32_t tS = tmem + kColS0 + (ps.slot >= kDepth ? ps.slot - kDepth : ps.slot) * kColSStride;
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const int c = k >> 2, kk = k & 3;
-                    umma_ss(tS, dQ + ((c * (kBT * 128) + kk * 32) >> 4), dku + ((c * 2 * L::kWChunk + kk * 32) >> 4),
-                            idesc1, k > 0 ? 1u : 0u);
+                    umma_ts(tS, tQ + k * 8, dku + ((c * 2 * L::kWChunk + kk * 32) >> 4), idesc1, k > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(BAR_KUEMPTY + pw.slot));
-                umma_commit(bar(BAR_SFULL + ps.slot));
+                umma_commit(bar(BAR_SFULL + sb));
                 pw.advance(2);
-                ps.advance(2);
-                pf.advance(2);
             }
         }
     } else if (warp == 3) {
         // ------------------------------------------------------------------ MMA issuer 2: O += A V
-        // A comes from tensor memory (the first 32 columns of the block's S buffer), V from shared
-        // memory as an MN-major operand.
+        // A comes from tensor memory (slot block % 2), V from shared memory as an MN-major operand.
         if (lane == 0) {
             constexpr uint32_t idesc2 = umma_idesc(128, DH, false, true);
             const uint64_t dV0 = desc_mnmajor(sV, L::kWChunk);
             constexpr uint64_t kVStep = L::kVStage >> 4;
             RingPos<kRing> pw;
-            RingPos<kSBars> ps;
             bool ok = true;
             for (int j = 0; j < nblk; ++j) {
+                const int slot = j & 1;
                 if (!mbar_wait(bar(BAR_VFULL + pw.slot), pw.lap, ctl, W + 6)) { ok = false; break; }
-                if (!mbar_wait(bar(BAR_AFULL + ps.slot), ps.lap, ctl, W + 7)) { ok = false; break; }
+                if (!mbar_wait(bar(BAR_AFULL + slot), (j >> 1) & 1, ctl, W + 7)) { ok = false; break; }
                 tc_fence_after();
                 const uint64_t dv = dV0 + pw.slot * kVStep;
-                const uint32_t tA = tmem + kColS0 + (ps.slot >= kDepth ? ps.slot - kDepth : ps.slot) * kColSStride;
+                const uint32_t tA = tmem + kColA0 + slot * kColAStride;
 #pragma unroll
                 for (int k = 0; k < kBI / 16; ++k)
                     umma_ts(tmem + kColO, tA + k * 8, dv + k * 128, idesc2, (j > 0 || k > 0) ? 1u : 0u);
                 umma_commit(bar(BAR_VEMPTY + pw.slot));
-                umma_commit(bar(BAR_SFREE + ps.slot));
+                umma_commit(bar(BAR_AFREE + slot));
                 pw.advance(1);
-                ps.advance(1);
             }
             if (ok) umma_commit(bar(BAR_OFULL));
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ activation + epilogue
-        const int quarter = warp & 3, group = (warp - 4) >> 2;  // group 0: even blocks, group 1: odd blocks
+        const int quarter = warp & 3, team = (warp - 4) >> 3, group = ((warp - 4) >> 2) & 1;  // group = column half
         const int row = quarter * 32 + lane;
         const int t = t0 + row;
         const bool in_range = t < args.S;
@@ -253,39 +255,59 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
         bool ok = true;
         const f32x2 half_s0 = f2_pack(args.half_s0, args.half_s0);
-        // sub-network of this group's current block and position inside it; routing weight fetched a block ahead
-        int e = (j0 + group) / blocks_per_e, in_e = (j0 + group) - e * blocks_per_e;
+        // Q: shared -> tensor memory, once, by team 0 (thread = token row; its lower four warps copy columns [0, 64)
+        // of d_h, the upper four [64, 128)).
+        if (team == 0) {
+            if (!mbar_wait(bar(BAR_Q), 0, ctl, W + 11)) ok = false;
+            if (ok && group * 64 < DH) {
+                uint32_t qv[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(gbase + L::kOffQ + group * (kBT * 128) + sw128_offset(row, c));
+                    qv[4 * c] = v.x; qv[4 * c + 1] = v.y; qv[4 * c + 2] = v.z; qv[4 * c + 3] = v.w;
+                }
+                tmem_st32(lane_base + kColQ + group * 32, qv);
+                tmem_st_wait();
+            }
+            tc_fence_before();
+            warp_arrive(bar(BAR_QT));
+        }
+        // sub-network of this team's current block and position inside it; the routing weight is fetched one ahead
+        int e = (j0 + team) / blocks_per_e, in_e = (j0 + team) - e * blocks_per_e;
         float r_cur = (in_range && e < args.E) ? __ldg(rrow + e) : 0.f;
-        RingPos<kSBars> p;
-        p.advance(group);
-        for (int j = group; j < nblk; j += 2) {
-            int e_nb = e, in_nb = in_e + 2;  // where this group's next block lies
-            while (in_nb >= blocks_per_e) { in_nb -= blocks_per_e; ++e_nb; }
-            const float r_nb = (e_nb != e && in_range && e_nb < args.E) ? __ldg(rrow + e_nb) : r_cur;
+        float r_next = (in_range && e + 1 < args.E) ? __ldg(rrow + e + 1) : 0.f;
+        for (int j = team; ok && j < nblk; j += kTeams) {
+            const int sb = j & 1;   // S buffer and A slot of this block
             const float hr = 0.5f * args.c * r_cur;
             const f32x2 half_r = f2_pack(hr, hr);
-            if (!mbar_wait(bar(BAR_SFULL + p.slot), p.lap, ctl, W + 8)) { ok = false; break; }
+            if (!mbar_wait(bar(BAR_SFULL + sb), (j >> 1) & 1, ctl, W + 8)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t ts = lane_base + kColS0 + (p.slot >= kDepth ? p.slot - kDepth : p.slot) * kColSStride;
-            uint32_t a[32];  // 64 bf16 of this row of A
+            const uint32_t ts = lane_base + kColS0 + sb * kColSStride + group * 32;
+            uint32_t m[32], n[32], a[16];  // this thread's 32 columns of M and of N; 32 bf16 of A
+            tmem_ld32x2_sync(ts, ts + kBI, m, n);
+            tc_fence_before();
+            warp_arrive(bar(BAR_SEMPTY + sb));  // S is in registers: the buffer may take block j + 2
 #pragma unroll
-            for (int part = 0; part < 2; ++part) {
-                uint32_t m[32], n[32];
-                tmem_ld32x2_sync(ts + part * 32, ts + kBI + part * 32, m, n);
-#pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    a[part * 16 + i] = fwd_act_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]),
-                                                    f2_pack_bits(n[2 * i], n[2 * i + 1]), half_r, half_s0);
-            }
-            tmem_st32(ts, a);  // over M[0:32] of this buffer, which is in registers by now
+            for (int i = 0; i < 16; ++i)
+                a[i] = fwd_act_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]), f2_pack_bits(n[2 * i], n[2 * i + 1]), half_r,
+                                    half_s0);
+            // the slot's previous block (j - 2) has been consumed by its O update
+            if (j >= 2 && !mbar_wait(bar(BAR_AFREE + sb), ((j >> 1) - 1) & 1, ctl, W + 9)) { ok = false; break; }
+            tc_fence_after();
+            tmem_st16(lane_base + kColA0 + sb * kColAStride + group * 16, a);
             tmem_st_wait();
             tc_fence_before();
-            warp_arrive(bar(BAR_AFULL + p.slot));
-            p.advance(2);
-            r_cur = r_nb;
-            e = e_nb;
-            in_e = in_nb;
+            warp_arrive(bar(BAR_AFULL + sb));
+#pragma unroll
+            for (int k = 0; k < kTeams; ++k)
+                if (++in_e == blocks_per_e) {
+                    in_e = 0;
+                    ++e;
+                    r_cur = r_next;
+                    r_next = (in_range && e + 1 < args.E) ? __ldg(rrow + e + 1) : 0.f;
+                }
         }
+        if (team != 0) ok = false;   // the epilogue is team 0's
         // epilogue: O (fp32, tensor memory) -> bf16 -> shared (over the Q tile) -> TMA store
         if (ok) ok = mbar_wait(bar(BAR_OFULL), 0, ctl, W + 10);
         if (ok && args.nsplit > 1) {
@@ -328,7 +350,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             tc_fence_before();
             fence_async_smem();
         }
-        named_bar_sync(1, 2 * kGroupThreads);
+        if (team == 0) named_bar_sync(1, kTeamThreads);
         if (ok && args.nsplit == 1 && warp == 4 && lane == 0 && !*abort_flag) {
             for (int c = 0; c < L::kChunks; ++c) tma_store_4d(&tmO, sQ + c * (kBT * 128), c * 64, t0, h, b);
             tma_store_commit();
@@ -431,7 +453,7 @@ int launch_fwd(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
               p.scale.head_scaling * p.scale.up_scaling * p.scale.final_scaling, wait_args(dc)};
     dim3 grid(((p.d.S + kBT - 1) / kBT) * pl.nsplit, p.d.H, p.d.B);
     prof_mark(st, kMarkStart);
-    fwd_kernel<DH><<<grid, kThreads, L::kTotal, st>>>(tmQ, tmK, tmU, tmV, tmO, a);
+    fwd_kernel<DH><<<grid, threads_for(DH), L::kTotal, st>>>(tmQ, tmK, tmU, tmV, tmO, a);
     prof_mark(st, kMarkFwd);
     *n_launch += 1;
     cudaError_t e = cudaGetLastError();

@@ -1,7 +1,8 @@
 """Operator and LM measurements beyond the one line bench.py prints.
 
-    python -m flashmhf_b200.opbench --sweep      # operator forward+backward over a grid of shapes, next to a dense SwiGLU
-    python -m flashmhf_b200.opbench --lm         # forward tokens/s of the 128M and 1.3B LMs, training step of the 370M LM
+    python opbench.py --sweep      # operator forward+backward over a grid of shapes, next to a dense SwiGLU and the eager path on the GPU
+    python opbench.py --lm         # forward tokens/s of the 128M and 1.3B LMs, training step of the 370M LM
+    python opbench.py --decode     # decode-shaped forward calls (a few tokens, weights streamed from HBM)
 
 Everything is timed with CUDA events after warm-up; inputs are seeded synthetic tensors (Q ~ N(0,1),
 weights ~ N(0, 0.02), routing weights = normalised sigmoid of N(0,1) logits, dO ~ N(0,1)).
@@ -12,16 +13,20 @@ Prints markdown tables.
 import argparse
 import json
 import os
+import sys
 
-import torch
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
 
 NOMINAL_TFLOPS = 2250.0
 
 
 def _measured_sustained():
-    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     try:
-        with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             return float(json.load(f)["bf16_tflops_sustained"])
     except (OSError, KeyError, ValueError):
         return 1400.0
@@ -46,8 +51,8 @@ def sweep(args):
     from flashmhf_b200 import _lib
     sustained = _measured_sustained()
     dev = torch.device("cuda")
-    print("| T | d_h | H | E | d_e | fwd ms | bwd ms | TFLOP/s | of nominal 2250 | of measured %.0f | peak MB | dense SwiGLU TFLOP/s | ratio |" % sustained)
-    print("|---|---|---|---|---|---|---|---|---|---|---|---|---|")
+    print("| T | d_h | H | E | d_e | fwd ms | bwd ms | TFLOP/s | of nominal 2250 | of measured %.0f | peak MB | dense SwiGLU TFLOP/s | ratio | eager-on-GPU TFLOP/s |" % sustained)
+    print("|---|---|---|---|---|---|---|---|---|---|---|---|---|---|")
     shapes = []
     for dh, des in ((128, (320, 256)), (64, (192,))):
         for de in des:
@@ -85,8 +90,22 @@ def sweep(args):
             X.grad = Wg.grad = Wu.grad = Wd.grad = None
         td = _time(dense)
         tfd = flops / (td * 1e-3) / 1e12
+        # harness-side comparator: the reference's eager loop (the CPU oracle's restatement of it) run on the GPU in
+        # bf16 with autograd -- what the reference layer does with use_flash=False; only where its [T, d_e]
+        # intermediates fit comfortably
+        tfe = None
+        if T * H * de * 2 * 8 * E < 40e9:
+            from oracle import mhffn_oracle as orc
+            ins = [t.detach().clone().requires_grad_(True) for t in (Q, K, U, V, R)]
+
+            def eager():
+                orc.mhffn_forward(*ins).backward(dO)
+                for t in ins:
+                    t.grad = None
+            tfe = flops / (_time(eager) * 1e-3) / 1e12
+            del ins
         print(f"| {T} | {dh} | {H} | {E} | {de} | {tf:.3f} | {tb:.3f} | {tfl:.0f} | {tfl / NOMINAL_TFLOPS:.3f} | {tfl / sustained:.3f} | "
-              f"{peak:.0f} | {tfd:.0f} | {tfl / tfd:.2f} |", flush=True)
+              f"{peak:.0f} | {tfd:.0f} | {tfl / tfd:.2f} | {'-' if tfe is None else format(tfe, '.0f')} |", flush=True)
         del Q, dO, K, U, V, R, X, Wg, Wu, Wd, gO
         torch.cuda.empty_cache()
 
@@ -123,18 +142,83 @@ def lm_runs(args):
     print(f"\npeak memory of the 370M training step: {torch.cuda.max_memory_allocated() / 2**30:.1f} GiB")
 
 
+def decode_runs(args):
+    """Decode-shaped forward calls: B sequences, one new token each.  The weights of 8 layers are cycled so that every
+    call streams its K, U, V from HBM (one layer's weights would stay in L2).  Reported per layer call: time from Python
+    (host launch included), kernel-only time from CUDA events, and the same calls replayed from a CUDA graph; GB/s is
+    the layer's weight bytes over that time (algorithmic bytes of the call: 6*H*E*d_e*d_h, Q/O/R are negligible)."""
+    import flashmhf_b200 as fm
+    from flashmhf_b200 import _lib
+    hbm = 6547.0
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            hbm = float(json.load(f)["hbm_gbs"])
+    except (OSError, KeyError, ValueError):
+        pass
+    print(f"| shape | weights MB | python call us | kernels us (fwd + reduce) | fwd kernel GB/s | of measured {hbm:.0f} | graph replay us | graph GB/s |")
+    print("|---|---|---|---|---|---|---|---|")
+    for (B, H, E, de, dh, name) in [(64, 16, 22, 256, 128, "1.3B layer, 64 tokens"), (8, 16, 22, 256, 128, "1.3B layer, 8 tokens"),
+                                    (64, 8, 11, 256, 128, "370M layer, 64 tokens")]:
+        g = torch.Generator(device="cuda").manual_seed(0)
+        Q = torch.randn(B, H, 1, dh, device="cuda", generator=g).bfloat16()
+        Ws = [[torch.randn(H, E, de, dh, device="cuda", generator=g).mul(0.02).bfloat16() for _ in range(3)] for _ in range(8)]
+        R = torch.rand(B, H, 1, E, device="cuda", generator=g)
+        for i in range(8):
+            fm.forward_raw(Q, *Ws[i], R)
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        n = 80
+        ev[0].record()
+        for i in range(n):
+            fm.forward_raw(Q, *Ws[i % 8], R)
+        ev[1].record()
+        torch.cuda.synchronize()
+        call_us = ev[0].elapsed_time(ev[1]) / n * 1e3
+        wbytes = 3 * H * E * de * dh * 2
+        _lib.profile_begin(1024)
+        for i in range(n):
+            fm.forward_raw(Q, *Ws[i % 8], R)
+        k = _lib.profile_end()
+        _lib.device_status()
+        fwd_us = sum(k["fwd_kernel"]) / len(k["fwd_kernel"]) * 1e3
+        red_us = sum(k.get("o_reduce_kernel", [0.0])) / max(1, len(k.get("o_reduce_kernel", []))) * 1e3
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(8):
+                fm.forward_raw(Q, *Ws[i], R)
+        torch.cuda.current_stream().wait_stream(side)
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            outs = [fm.forward_raw(Q, *Ws[i], R) for i in range(8)]
+        gr.replay()
+        torch.cuda.synchronize()
+        ev[0].record()
+        for _ in range(10):
+            gr.replay()
+        ev[1].record()
+        torch.cuda.synchronize()
+        graph_us = ev[0].elapsed_time(ev[1]) / 80 * 1e3
+        print(f"| {name} | {wbytes / 1e6:.1f} | {call_us:.1f} | {fwd_us:.1f} + {red_us:.1f} | {wbytes / fwd_us / 1e3:.0f} | "
+              f"{wbytes / fwd_us / 1e3 / hbm:.2f} | {graph_us:.1f} | {wbytes / graph_us / 1e3:.0f} |", flush=True)
+        del outs, gr, Ws
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--sweep", action="store_true")
     ap.add_argument("--lm", action="store_true")
+    ap.add_argument("--decode", action="store_true")
     ap.add_argument("--quick", action="store_true", help="a quarter of the sweep grid")
     args = ap.parse_args()
-    if not (args.sweep or args.lm):
-        ap.error("choose --sweep and/or --lm")
+    if not (args.sweep or args.lm or args.decode):
+        ap.error("choose --sweep, --lm and/or --decode")
     if args.sweep:
         sweep(args)
     if args.lm:
         lm_runs(args)
+    if args.decode:
+        decode_runs(args)
 
 
 if __name__ == "__main__":
