@@ -106,13 +106,17 @@ int check_tensor(const flashmhf_tensor &t, unsigned align = 16) {
 }
 
 int check_arch() {
+    static std::atomic<int> major_of[kMaxDevices];   // 0 = not asked yet
     int dev = 0, major = 0;
     cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess && dev >= 0 && dev < kMaxDevices && (major = major_of[dev].load(std::memory_order_relaxed)) != 0)
+        return major == 10 ? FLASHMHF_OK : FLASHMHF_ERR_ARCH;
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
     if (e != cudaSuccess) {
         set_cuda_error(e, "device query");
         return FLASHMHF_ERR_CUDA;
     }
+    if (dev >= 0 && dev < kMaxDevices) major_of[dev].store(major, std::memory_order_relaxed);
     return major == 10 ? FLASHMHF_OK : FLASHMHF_ERR_ARCH;
 }
 

@@ -6,11 +6,11 @@
 //
 // Two kernels, each the sole owner of its accumulators (no floating-point atomics, bit-reproducible):
 //
-// bwd_dq_kernel  -- token-stationary.  One CTA owns 128 token rows of one (batch, head): Q and dO
-//   tiles stay in shared memory, the head's weights stream through (K/U ring of 3, V ring of 2).
-//   Tensor memory: dQ accumulator + two buffers of {S = [M|N] (128 cols), dA (64 cols)}; the bf16
-//   [dM|dN] operand of the dQ update is written back over the dA columns and read from there.
-//   Produces dQ (TMA store) and dR (direct stores).
+// bwd_dq_kernel  -- token-stationary.  One CTA owns 128 token rows of one (batch, head): its Q and dO
+//   tiles are copied once into tensor memory and all three MMA chains read their A operand from there,
+//   the head's weights stream through shared memory (K/U ring of 3, V ring of 2).
+//   Tensor memory: dQ accumulator (128 cols), Q and dO as bf16 (64 + 64), S = [M|N] (128), dA (64), and the
+//   bf16 [dM|dN] operand of the dQ update (64).  Produces dQ (TMA store) and dR (direct stores).
 //
 // bwd_dw_kernel  -- weight-stationary.  One CTA owns one 64-row block of K, U and V of one K/U/V
 //   head and a contiguous range of token tiles (the token axis is split `nsplit` ways to fill the
@@ -96,8 +96,13 @@ struct DqSmem {
     static constexpr uint32_t kTotal = kOffCtl + kCtlBytes + 1024;
 };
 
-enum { DQ_QFULL = 0, DQ_KUFULL = 1, DQ_KUEMPTY = 4, DQ_VFULL = 7, DQ_VEMPTY = 9, DQ_SFULL = 11, DQ_SEMPTY = 13,
-       DQ_PFULL = 15, DQ_ACCFULL = 17, DQ_DRFULL = 18, DQ_DAFREE = 20, DQ_DRFREE = 22, DQ_BARS = 24 };
+// Barriers.  Q and dO are copied once into tensor memory (QT); S, dA and the [dM|dN] operand each have ONE buffer
+// there, because the accumulator, Q and dO take half of tensor memory:
+//   SFULL (S and dA of the block computed: one commit from each of their issuers), SEMPTY (both are in the
+//   element-wise warps' registers), PFULL ([dM|dN] written), PEMPTY (the dQ update that read it is done).
+// All of them complete once per block and every waiter waits on every phase, so a one-bit parity is enough.
+enum { DQ_QFULL = 0, DQ_KUFULL = 1, DQ_KUEMPTY = 4, DQ_VFULL = 7, DQ_VEMPTY = 9, DQ_SFULL = 11, DQ_SEMPTY = 12,
+       DQ_PFULL = 13, DQ_PEMPTY = 14, DQ_ACCFULL = 15, DQ_QT = 16, DQ_DRFULL = 18, DQ_DRFREE = 20, DQ_BARS = 22 };
 
 struct DqArgs {
     const float *R;
@@ -123,7 +128,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
                    sBar = base + L::kOffCtl;
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gbase + L::kOffCtl + DQ_BARS * 8);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(gbase + L::kOffCtl + DQ_BARS * 8 + 4);
-    volatile float *drx = reinterpret_cast<volatile float *>(gbase + L::kOffCtl + 256);  // [2][128]
+    volatile float *drx = reinterpret_cast<volatile float *>(gbase + L::kOffCtl + 256);  // [2][kParts - 1][128]
     auto bar = [&](int i) { return sBar + 8u * i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,18 +136,20 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     const int bpe = args.De / kBI, nblk = args.E * bpe;
     const WaitCtl ctl{abort_flag, args.wait};
     constexpr int W = kKernelBwdDq * 100;
-    constexpr uint32_t kColAcc = 0, kColS0 = 128, kBufStride = 192, kColdA = 128;  // dA offset inside a buffer
+    // Tensor memory: dQ accumulator, Q and dO as bf16 A operands (64 columns each), S = [M | N], dA, [dM | dN] (bf16).
+    constexpr uint32_t kColAcc = 0, kColQ = 128, kColdO = 192, kColS = 256, kColdA = 384, kColP = 448;
 
     if (threadIdx.x == 0) {
         *abort_flag = launch_aborted(args.wait);  // a CTA of this launch gave up: drain fast
         mbar_init(bar(DQ_QFULL), 1);
         for (int s = 0; s < L::kKUStages; ++s) { mbar_init(bar(DQ_KUFULL + s), 1); mbar_init(bar(DQ_KUEMPTY + s), 1); }
         for (int s = 0; s < L::kVStages; ++s) { mbar_init(bar(DQ_VFULL + s), 1); mbar_init(bar(DQ_VEMPTY + s), 1); }
+        mbar_init(bar(DQ_SFULL), 2);                          // one commit from each of the two recompute issuers
+        mbar_init(bar(DQ_SEMPTY), arrivals_of(kActThreads));  // S and dA are in registers
+        mbar_init(bar(DQ_PFULL), arrivals_of(kActThreads));   // [dM|dN] written
+        mbar_init(bar(DQ_PEMPTY), 1);                         // the dQ update that read [dM|dN] is done
+        mbar_init(bar(DQ_QT), arrivals_of(kActThreads));      // Q and dO copied to tensor memory
         for (int i = 0; i < 2; ++i) {
-            mbar_init(bar(DQ_SFULL + i), 2);             // one commit from each of the two recompute issuers
-            mbar_init(bar(DQ_SEMPTY + i), arrivals_of(kActThreads));  // S and dA of the buffer are in registers
-            mbar_init(bar(DQ_PFULL + i), arrivals_of(kActThreads));   // [dM|dN] written over the dA columns
-            mbar_init(bar(DQ_DAFREE + i), 1);            // the dQ update that read [dM|dN] is done
             mbar_init(bar(DQ_DRFULL + i), arrivals_of(kActThreads - 128));  // column parts 1.. have written their dR_e partials
             mbar_init(bar(DQ_DRFREE + i), arrivals_of(128));                 // part 0 has read them: the rows may be reused
         }
@@ -191,60 +198,53 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             }
         }
     } else if (warp == 1) {
-        // Three MMA chains, three issuing threads (warps 1, 2, 3), so that none waits on another's
-        // barriers and the tensor pipe, which accepts MMAs only a few ahead of execution, is fed by
-        // whichever is ready.  Descriptors are built once and advanced by constants (16-byte units).
-        // Issuer 1: S = Q [K;U]^T.  Its buffer is free again as soon as the element-wise warps have
-        // read it, so this chain runs well ahead.
+        // Three MMA chains, three issuing threads (warps 1, 2, 3), so that none waits on another's barriers and the
+        // tensor pipe, which accepts MMAs only a few ahead of execution, is fed by whichever is ready.  Every chain
+        // reads its A operand from tensor memory: an MMA with both operands in shared memory takes the SM's whole
+        // shared-memory bandwidth (8 KB per 64 clk), which the weight tiles arriving by TMA need as well.
+        // Issuer 1: S = Q [K;U]^T.
         if (lane == 0) {
             constexpr uint32_t idS = umma_idesc(128, 2 * kBI, false, false);
-            const uint64_t dQd = desc_kmajor(sQ), dKU0 = desc_kmajor(sKU);
+            const uint64_t dKU0 = desc_kmajor(sKU);
             constexpr uint64_t kKUStep = L::kKUStage >> 4;
-            bool ok = mbar_wait(bar(DQ_QFULL), 0, ctl, W + 3);
+            bool ok = mbar_wait(bar(DQ_QT), 0, ctl, W + 3);
             int sk = 0;
             uint32_t phk = 0;
             for (int j = 0; ok && j < nblk; ++j) {
-                const int bb = j & 1;
                 if (!mbar_wait(bar(DQ_KUFULL + sk), phk, ctl, W + 4)) break;
-                if (!mbar_wait(bar(DQ_SEMPTY + bb), ((j >> 1) & 1) ^ 1, ctl, W + 5)) break;
+                if (j >= 1 && !mbar_wait(bar(DQ_SEMPTY), (j - 1) & 1, ctl, W + 5)) break;
                 tc_fence_after();
                 const uint64_t dku = dKU0 + sk * kKUStep;
-                const uint32_t tS = tmem + kColS0 + bb * kBufStride;
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const int c = k >> 2, kk = k & 3;
-                    umma_ss(tS, dQd + ((c * kTile + kk * 32) >> 4), dku + ((c * 2 * kWChunk + kk * 32) >> 4), idS,
-                            k > 0 ? 1u : 0u);
+                    umma_ts(tmem + kColS, tmem + kColQ + k * 8, dku + ((c * 2 * kWChunk + kk * 32) >> 4), idS, k > 0 ? 1u : 0u);
                 }
-                umma_commit(bar(DQ_SFULL + bb));
+                umma_commit(bar(DQ_SFULL));
                 if (++sk == L::kKUStages) { sk = 0; phk ^= 1; }
             }
         }
     } else if (warp == 2) {
-        // Issuer 2: dA = dO V^T.  The dA columns are reused for [dM|dN], so they are free only after the
-        // dQ update of the block that used them last.
+        // Issuer 2: dA = dO V^T.
         if (lane == 0) {
             constexpr uint32_t idA = umma_idesc(128, kBI, false, false);
-            const uint64_t dOd = desc_kmajor(sdO), dV0 = desc_kmajor(sV);
+            const uint64_t dV0 = desc_kmajor(sV);
             constexpr uint64_t kVStep = L::kVStage >> 4;
-            bool ok = mbar_wait(bar(DQ_QFULL), 0, ctl, W + 3);
+            bool ok = mbar_wait(bar(DQ_QT), 0, ctl, W + 3);
             int sv = 0;
             uint32_t phv = 0;
             for (int j = 0; ok && j < nblk; ++j) {
-                const int bb = j & 1;
                 if (!mbar_wait(bar(DQ_VFULL + sv), phv, ctl, W + 4)) break;
-                if (!mbar_wait(bar(DQ_DAFREE + bb), ((j >> 1) & 1) ^ 1, ctl, W + 5)) break;
+                if (j >= 1 && !mbar_wait(bar(DQ_SEMPTY), (j - 1) & 1, ctl, W + 5)) break;
                 tc_fence_after();
                 const uint64_t dv = dV0 + sv * kVStep;
-                const uint32_t tA = tmem + kColS0 + bb * kBufStride + kColdA;
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const int c = k >> 2, kk = k & 3;
-                    umma_ss(tA, dOd + ((c * kTile + kk * 32) >> 4), dv + ((c * kWChunk + kk * 32) >> 4), idA,
-                            k > 0 ? 1u : 0u);
+                    umma_ts(tmem + kColdA, tmem + kColdO + k * 8, dv + ((c * kWChunk + kk * 32) >> 4), idA, k > 0 ? 1u : 0u);
                 }
                 umma_commit(bar(DQ_VEMPTY + sv));
-                umma_commit(bar(DQ_SFULL + bb));
+                umma_commit(bar(DQ_SFULL));
                 if (++sv == L::kVStages) { sv = 0; phv ^= 1; }
             }
         }
@@ -257,23 +257,21 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
             int sk = 0;
             bool ok = true;
             for (int j = 0; j < nblk; ++j) {
-                const int bb = j & 1;
-                if (!mbar_wait(bar(DQ_PFULL + bb), (j >> 1) & 1, ctl, W + 6)) { ok = false; break; }
+                if (!mbar_wait(bar(DQ_PFULL), j & 1, ctl, W + 6)) { ok = false; break; }
                 tc_fence_after();
                 const uint64_t dku = dKUmn0 + sk * kKUStep;
-                const uint32_t tP = tmem + kColS0 + bb * kBufStride + kColdA;
-                // [dM|dN] sits over the 64 dA columns as packed bf16 pairs.  The thread that handled block columns
-                // [c, c + kCols) wrote its dM to dA columns [c, c + kCols/2) and its dN to [c + kCols/2, c + kCols) --
-                // columns only it had read.  K step k (16 values = 8 columns; steps 0-3 pair with the K rows of the
-                // stage, 4-7 with the U rows) covers block columns [16 (k%4), 16 (k%4) + 16).
+                // [dM|dN] as packed bf16 pairs in 64 columns.  The thread that handled block columns [c, c + kCols) wrote
+                // its dM to columns [c, c + kCols/2) and its dN to [c + kCols/2, c + kCols).  K step k (16 values = 8
+                // columns; steps 0-3 pair with the K rows of the stage, 4-7 with the U rows) covers block columns
+                // [16 (k%4), 16 (k%4) + 16).
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     const int bc = 16 * (k & 3);
                     const int col = (bc / kCols) * kCols + (bc % kCols) / 2 + (k >> 2) * (kCols / 2);
-                    umma_ts(tmem + kColAcc, tP + col, dku + k * 128, idQ, (j > 0 || k > 0) ? 1u : 0u);
+                    umma_ts(tmem + kColAcc, tmem + kColP + col, dku + k * 128, idQ, (j > 0 || k > 0) ? 1u : 0u);
                 }
                 umma_commit(bar(DQ_KUEMPTY + sk));
-                umma_commit(bar(DQ_DAFREE + bb));
+                umma_commit(bar(DQ_PEMPTY));
                 if (++sk == L::kKUStages) sk = 0;
             }
             if (ok) umma_commit(bar(DQ_ACCFULL));
@@ -285,52 +283,83 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
         const float *rrow = args.R + (long long)b * args.r_sb + (long long)h * args.r_sh + (long long)t * args.r_ss;
         float *drrow = args.dR + (long long)b * args.dr_sb + (long long)h * args.dr_sh + (long long)t * args.dr_ss;
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+        bool ok = true;
+        // Q and dO: shared -> tensor memory, once (thread = token row; column part p < 2 copies columns [64p, 64p + 64)
+        // of d_h of both tiles).
+        if (!mbar_wait(bar(DQ_QFULL), 0, ctl, W + 12)) ok = false;
+        if (ok && part < 2 && part * 64 < DH) {
+#pragma unroll
+            for (int which = 0; which < 2; ++which) {
+                uint32_t v32[32];
+                const uint8_t *src = gbase + (which ? L::kOffdO : L::kOffQ) + part * kTile;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = *reinterpret_cast<const uint4 *>(src + sw128_offset(row, c));
+                    v32[4 * c] = v.x; v32[4 * c + 1] = v.y; v32[4 * c + 2] = v.z; v32[4 * c + 3] = v.w;
+                }
+                tmem_st32(lane_base + (which ? kColdO : kColQ) + part * 32, v32);
+            }
+            tmem_st_wait();
+        }
+        tc_fence_before();
+        warp_arrive(bar(DQ_QT));
         float r_cur = 0.f, r_next = in_range ? __ldg(rrow) : 0.f;
         f32x2 dr2 = f2_pack(0.f, 0.f);  // running dR_e of this thread's columns (two interleaved partial sums)
         const BwdConst kc = bwd_const(args.s0);
-        bool ok = true;
         int in_e = 0, e = 0;  // block index inside the current sub-network; current sub-network
-        for (int j = 0; j < nblk; ++j) {
-            const int bb = j & 1, nb = j >> 1;
+        for (int j = 0; ok && j < nblk; ++j) {
             if (in_e == 0) {
                 r_cur = r_next;
                 r_next = (in_range && e + 1 < args.E) ? __ldg(rrow + e + 1) : 0.f;
                 dr2 = f2_pack(0.f, 0.f);
             }
-            if (!mbar_wait(bar(DQ_SFULL + bb), nb & 1, ctl, W + 7)) { ok = false; break; }
+            if (!mbar_wait(bar(DQ_SFULL), j & 1, ctl, W + 7)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t tS = lane_base + kColS0 + bb * kBufStride + part * kCols;
+            const uint32_t tS = lane_base + kColS + part * kCols, tA = lane_base + kColdA + part * kCols;
             uint32_t pm[kCols / 2], pn[kCols / 2];  // packed bf16 pairs of dM, dN for this thread's columns
             const f32x2 r2 = f2_pack(args.c * r_cur, args.c * r_cur);
+            if (kCols == 32) {
+                // the whole part at once, so that S and dA are free for the next block before any arithmetic
+                uint32_t m[32], n[32], da[32];
+                tmem_ld32x3_sync(tS, tS + kBI, tA, m, n, da);
+                tc_fence_before();
+                warp_arrive(bar(DQ_SEMPTY));
 #pragma unroll
-            for (int sub = 0; sub < kSubs; ++sub) {
-                uint32_t m[16], n[16], da[16];
-                tmem_ld16x3_sync(tS + sub * 16, tS + kBI + sub * 16, tS + kColdA + sub * 16, m, n, da);
-                if (sub == kSubs - 1) {   // S is in registers: it may be recomputed for block j+2 from here on
-                    tc_fence_before();
-                    warp_arrive(bar(DQ_SEMPTY + bb));
+                for (int i = 0; i < 16; ++i) {
+                    const BwdPair x = bwd_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]), f2_pack_bits(n[2 * i], n[2 * i + 1]),
+                                               f2_pack_bits(da[2 * i], da[2 * i + 1]), r2, kc);
+                    dr2 = f2_fma(x.da, x.sn, dr2);
+                    pm[i] = f2_to_bf16x2(x.dm);
+                    pn[i] = f2_to_bf16x2(x.dn);
                 }
+            } else {
+                uint32_t m[16], n[16], da[16];
+                tmem_ld16x3_sync(tS, tS + kBI, tA, m, n, da);
+                tc_fence_before();
+                warp_arrive(bar(DQ_SEMPTY));
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const BwdPair x = bwd_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]), f2_pack_bits(n[2 * i], n[2 * i + 1]),
                                                f2_pack_bits(da[2 * i], da[2 * i + 1]), r2, kc);
                     dr2 = f2_fma(x.da, x.sn, dr2);
-                    pm[sub * 8 + i] = f2_to_bf16x2(x.dm);
-                    pn[sub * 8 + i] = f2_to_bf16x2(x.dn);
+                    pm[i] = f2_to_bf16x2(x.dm);
+                    pn[i] = f2_to_bf16x2(x.dn);
                 }
             }
-            // dM and dN go back into tensor memory as packed bf16 pairs, over the dA columns this thread has just
-            // read (no other thread reads those columns)
+            // the dQ update of the previous block has read the [dM|dN] buffer
+            if (j >= 1 && !mbar_wait(bar(DQ_PEMPTY), (j - 1) & 1, ctl, W + 8)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t tP = lane_base + kColP + part * kCols;
             if (kCols == 32) {
-                tmem_st16(tS + kColdA, pm);
-                tmem_st16(tS + kColdA + 16, pn);
+                tmem_st16(tP, pm);
+                tmem_st16(tP + 16, pn);
             } else {
-                tmem_st8(tS + kColdA, pm);
-                tmem_st8(tS + kColdA + 8, pn);
+                tmem_st8(tP, pm);
+                tmem_st8(tP + 8, pn);
             }
             tmem_st_wait();
             tc_fence_before();
-            warp_arrive(bar(DQ_PFULL + bb));
+            warp_arrive(bar(DQ_PFULL));
             if (++in_e == bpe) {  // sub-network finished: add the column parts of dR_e, in part order
                 const int xb = e & 1;
                 float dr_lo, dr_hi;

@@ -408,11 +408,13 @@ struct FwdPlan {
 };
 // With fewer token tiles than about half the SMs (decode-shaped calls) the blocks of the intermediate
 // dimension are spread over several CTAs per tile so that the weights stream in at full machine rate.
+// All CTAs must run at once: one CTA per SM, so tiles * splits never exceeds the SM count (a second,
+// nearly empty wave would double the duration of a call that lasts tens of microseconds).
 FwdPlan fwd_plan(const flashmhf_dims &d, int num_sms) {
     const long long tiles = (long long)((d.S + kBT - 1) / kBT) * d.H * d.B;
     const int nblk = d.E * d.De / kBI;
     int ns = 1;
-    if (tiles < num_sms / 2) ns = (int)((num_sms + tiles - 1) / tiles);
+    if (tiles < num_sms / 2) ns = (int)(num_sms / tiles);
     if (ns > nblk) ns = nblk;
     FwdPlan p;
     p.blocks_per_split = (nblk + ns - 1) / ns;

@@ -15,7 +15,24 @@ _DT = {torch.bfloat16: _lib.BF16, torch.float32: _lib.F32_CHECK}
 
 
 def _tensor(t):
-    return _lib.Tensor(t.data_ptr(), (C.c_int64 * 3)(*t.stride()[:3]))
+    s = t.stride()
+    return _lib.Tensor(t.data_ptr(), (s[0], s[1], s[2]))
+
+
+class _on_device:
+    """`with torch.cuda.device(dev)` only when `dev` is not the current device already (the context manager costs
+    several microseconds a call, which matters for decode-shaped calls)."""
+
+    def __init__(self, dev):
+        self.ctx = None if dev.index is None or dev.index == torch.cuda.current_device() else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *a):
+        if self.ctx is not None:
+            self.ctx.__exit__(*a)
 
 
 def _strided_ok(t, is_weight, de):
@@ -105,7 +122,7 @@ def forward_raw(Q, K, U, V, R, out=None, scaling=_lib.NO_SCALING):
     ws = torch.empty(nbytes, dtype=torch.uint8, device=Q.device) if nbytes else None
     p = _lib.FwdParams(d, _tensor(Qk), _tensor(K), _tensor(U), _tensor(V), _tensor(Rk), _tensor(Ok),
                        ws.data_ptr() if nbytes else None, nbytes, sc)
-    with torch.cuda.device(Q.device):
+    with _on_device(Q.device):
         _lib.check(lib.flashmhf_forward(C.byref(p), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return O
 
@@ -126,7 +143,7 @@ def backward_raw(Q, K, U, V, R, dO, scaling=_lib.NO_SCALING, parts="all", weight
     Q, K, U, V = _prep(Q), _prep(K, True, de), _prep(U, True, de), _prep(V, True, de)
     dO = _prep(dO.to(Q.dtype))
     R = _routing(R)
-    none = _lib.Tensor(None, (C.c_int64 * 3)(0, 0, 0))
+    none = _lib.Tensor(None, (0, 0, 0))
     dQ = dR = dK = dU = dV = None
     tQ = tR = tK = tU = tV = none
     ws_ptr, nbytes = None, 0
@@ -153,7 +170,7 @@ def backward_raw(Q, K, U, V, R, dO, scaling=_lib.NO_SCALING, parts="all", weight
     mask = {"all": 0, "inputs": _lib.BWD_INPUTS, "weights": _lib.BWD_WEIGHTS}[parts]
     p = _lib.BwdParams(d, _tensor(Q), _tensor(K), _tensor(U), _tensor(V), _tensor(R), _tensor(dO), tQ, tK, tU, tV, tR,
                        ws_ptr, nbytes, sc, mask)
-    with torch.cuda.device(Q.device):
+    with _on_device(Q.device):
         _lib.check(lib.flashmhf_backward(C.byref(p), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
     return dQ, dK, dU, dV, dR
 
