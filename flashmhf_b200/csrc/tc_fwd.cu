@@ -40,7 +40,12 @@ namespace {
 constexpr int kBT = 128;  // token rows per tile
 constexpr int kBI = 64;   // intermediate rows per block
 constexpr int kSBufs = 2;   // S buffers in tensor memory
-constexpr int kRing = 4;    // shared-memory stages of the [K;U] ring and of the V ring
+// Shared-memory stages of the [K;U] ring and of the V ring (two Q tiles take the rest).  The [K;U] ring must have an
+// EVEN number of stages: its "full" barriers are waited on by the two S issuers, which own alternate blocks, and a
+// barrier's phase is tracked with one parity bit, so each stage must always be waited on by the same issuer (with an
+// odd ring an issuer would meet a stage only every other time it fills and could take an old phase for the new one).
+constexpr int kKURing = 4, kVRing = 2;
+static_assert(kKURing % 2 == 0, "each [K;U] stage must belong to one S issuer");
 // Activation teams of eight warps (warp % 4 = lane quarter, next bit = which 32 of a block's 64 columns).  With two
 // teams, team t owns the blocks j = t (mod 2) and with them S buffer t and A slot t; the two teams are then in
 // different phases of their loop (wait, load, arithmetic, store), which keeps the arithmetic pipes busy.
@@ -55,35 +60,39 @@ constexpr uint32_t kColO = 0, kColQ = 128, kColA0 = 192, kColAStride = 32, kColS
 template <int DH>
 struct FwdSmem {
     static constexpr int kChunks = (DH + 63) / 64;              // 64-column SW128 chunks per row of d_h
-    static constexpr uint32_t kQBytes = kChunks * kBT * 128;    // Q tile (also the O staging tile)
+    static constexpr uint32_t kQBytes = kChunks * kBT * 128;    // one Q tile (also the O staging tile of its work item)
     static constexpr uint32_t kWChunk = kBI * 128;              // one 64-row x 64-col weight chunk
     static constexpr uint32_t kKUStage = 2 * kChunks * kWChunk; // per chunk: K rows then U rows = one 128-row K-major tile
     static constexpr uint32_t kVStage = kChunks * kWChunk;
     // offsets from the 1024-aligned base
-    static constexpr uint32_t kOffQ = 0;
-    static constexpr uint32_t kOffKU = kOffQ + kQBytes;
-    static constexpr uint32_t kOffV = kOffKU + kRing * kKUStage;
-    static constexpr uint32_t kOffBar = kOffV + kRing * kVStage;
+    static constexpr uint32_t kOffQ = 0;                        // two Q tiles: work items alternate between them
+    static constexpr uint32_t kOffKU = kOffQ + 2 * kQBytes;
+    static constexpr uint32_t kOffV = kOffKU + kKURing * kKUStage;
+    static constexpr uint32_t kOffBar = kOffV + kVRing * kVStage;
     static constexpr uint32_t kTotal = kOffBar + 320 + 1024;  // + barriers/control + alignment slack
 };
 
 // barrier slots (8 bytes each) inside the control area
+// QFULL[q]: Q tile q has landed; QFREE[q]: the O tile staged over it has been read by its TMA store;
 // SFULL[b]: S computed into buffer b; SEMPTY[b]: every warp of the team working on it has its part in registers;
-// AFULL[s]: A written to slot s; AFREE[s]: the O update that read slot s is done; QT: Q copied to tensor memory.
-// Buffer and slot of block j are j % 2, so every barrier is used once every two blocks and each has one fixed set
-// of waiters that observes each of its phases: a one-bit phase parity is enough.
-enum { BAR_Q = 0, BAR_KUFULL = 1, BAR_KUEMPTY = 5, BAR_VFULL = 9, BAR_VEMPTY = 13, BAR_SFULL = 17, BAR_SEMPTY = 19,
-       BAR_AFULL = 21, BAR_AFREE = 23, BAR_OFULL = 25, BAR_QT = 26, BAR_COUNT = 27 };
+// AFULL[s]: A written to slot s; AFREE[s]: the O update that read slot s is done; QT: Q copied to tensor memory;
+// OFULL: the last O update of a work item is done; OFREE: its accumulator has been read out.
+// A CTA walks several work items (token tiles); blocks are counted through all of them (g), buffer and slot of a block
+// are g % 2, Q tile and per-item barriers alternate with the item count, so every barrier has one fixed set of
+// waiters that observes each of its phases and a one-bit phase parity is enough.
+enum { BAR_QFULL = 0, BAR_QFREE = 2, BAR_KUFULL = 4, BAR_KUEMPTY = 8, BAR_VFULL = 12, BAR_VEMPTY = 16, BAR_SFULL = 20,  // rings: up to 4 stages
+       BAR_SEMPTY = 22, BAR_AFULL = 24, BAR_AFREE = 26, BAR_OFULL = 28, BAR_OFREE = 29, BAR_QT = 30, BAR_COUNT = 31 };
 
 struct FwdArgs {
     const float *R;
     long long r_sb, r_sh, r_ss;
     int S, E, De, G;
-    // Split of the intermediate dimension over CTAs (short token counts, e.g. decode): CTA x handles
-    // blocks [isplit * blocks_per_split, ...) of tile x / nsplit and writes an fp32 partial O.
+    // Split of the intermediate dimension over CTAs (short token counts, e.g. decode): a work item is (token tile,
+    // split) and covers blocks [isplit * blocks_per_split, ...) of the tile; it writes an fp32 partial O.
     int nsplit, blocks_per_split;
     float *part;           // [nsplit][B][H][S][DH] fp32, used when nsplit > 1
-    int H;
+    int H, B;
+    int tiles_per_seq, n_items;   // work items = tiles_per_seq * H * B * nsplit, dealt round-robin to the CTAs
     float half_s0;  // 0.5 * head_scaling: tanh argument scale, sigmoid(s0 m) = 0.5 + 0.5 tanh(0.5 s0 m)
     float c;        // head_scaling * up_scaling * final_scaling, folded into the routing weight
     WaitArgs wait;
@@ -99,6 +108,23 @@ struct RingPos {
         if (slot >= N) { slot -= N; lap ^= 1; }
     }
 };
+
+// A work item: which token tile of which (batch, head), which blocks of the intermediate dimension.
+struct FwdItem {
+    int t0, h, b, isplit, j0, nblk;
+};
+__device__ __forceinline__ FwdItem fwd_item(const FwdArgs &a, int item, int nblk_total) {
+    FwdItem w;
+    w.isplit = item % a.nsplit;
+    int t = item / a.nsplit;
+    w.t0 = (t % a.tiles_per_seq) * kBT;
+    t /= a.tiles_per_seq;
+    w.h = t % a.H;
+    w.b = t / a.H;
+    w.j0 = w.isplit * a.blocks_per_split;
+    w.nblk = min(nblk_total - w.j0, a.blocks_per_split);
+    return w;
+}
 
 template <int DH>
 __global__ void __launch_bounds__(threads_for(DH), 1)
@@ -117,30 +143,30 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     auto bar = [&](int i) { return sBar + 8u * i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x / args.nsplit, isplit = blockIdx.x - tile * args.nsplit;
-    const int t0 = tile * kBT, h = blockIdx.y, b = blockIdx.z, hk = h / args.G;
-    const int blocks_per_e = args.De / kBI;
-    const int j0 = isplit * args.blocks_per_split;                          // first block of this CTA
-    const int nblk = min(args.E * blocks_per_e - j0, args.blocks_per_split);  // blocks of this CTA (>= 1)
+    const int blocks_per_e = args.De / kBI, nblk_total = args.E * blocks_per_e;
     const WaitCtl ctl{abort_flag, args.wait};
     constexpr int W = kKernelFwd * 100;
 
     if (threadIdx.x == 0) {
         *abort_flag = launch_aborted(args.wait);  // a CTA of this launch gave up: drain fast
-        mbar_init(bar(BAR_Q), 1);
-        for (int i = 0; i < kRing; ++i) {
-            mbar_init(bar(BAR_KUFULL + i), 1);
-            mbar_init(bar(BAR_KUEMPTY + i), 1);
-            mbar_init(bar(BAR_VFULL + i), 1);
-            mbar_init(bar(BAR_VEMPTY + i), 1);
-        }
-        for (int i = 0; i < kSBufs; ++i) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar(BAR_QFULL + i), 1);
+            mbar_init(bar(BAR_QFREE + i), 1);
             mbar_init(bar(BAR_SFULL + i), 1);
             mbar_init(bar(BAR_SEMPTY + i), arrivals_of(kTeamThreads));
             mbar_init(bar(BAR_AFULL + i), arrivals_of(kTeamThreads));
             mbar_init(bar(BAR_AFREE + i), 1);
         }
+        for (int i = 0; i < kKURing; ++i) {
+            mbar_init(bar(BAR_KUFULL + i), 1);
+            mbar_init(bar(BAR_KUEMPTY + i), 1);
+        }
+        for (int i = 0; i < kVRing; ++i) {
+            mbar_init(bar(BAR_VFULL + i), 1);
+            mbar_init(bar(BAR_VEMPTY + i), 1);
+        }
         mbar_init(bar(BAR_OFULL), 1);
+        mbar_init(bar(BAR_OFREE), arrivals_of(kTeamThreads));
         mbar_init(bar(BAR_QT), arrivals_of(kTeamThreads));
         fence_mbar_init();
     }
@@ -160,110 +186,130 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             tma_prefetch_desc(&tmK);
             tma_prefetch_desc(&tmU);
             tma_prefetch_desc(&tmV);
-            mbar_arrive_expect_tx(bar(BAR_Q), L::kQBytes);
-            for (int c = 0; c < L::kChunks; ++c) tma_load_4d(sQ + c * (kBT * 128), &tmQ, bar(BAR_Q), c * 64, t0, h, b);
-            // [K;U] of block j, then V of block j-2: V is consumed about two blocks later than K and U of
-            // the same block, so with this lag the producer never waits on the V ring while a [K;U]
-            // stage is free.
-            RingPos<kRing> pk, pv;
-            for (int j = 0; j < nblk + 2; ++j) {
-                if (j < nblk) {
-                    if (!mbar_wait(bar(BAR_KUEMPTY + pk.slot), pk.lap ^ 1, ctl, W + 1)) break;
-                    const uint32_t fku = bar(BAR_KUFULL + pk.slot), dku = sKU + pk.slot * L::kKUStage;
-                    mbar_arrive_expect_tx(fku, L::kKUStage);
+            RingPos<kKURing> pk;
+            RingPos<kVRing> pv;
+            bool ok = true;
+            int n = 0;  // work items of this CTA so far
+            for (int item = blockIdx.x; ok && item < args.n_items; item += gridDim.x, ++n) {
+                const FwdItem w = fwd_item(args, item, nblk_total);
+                const int hk = w.h / args.G, q = n & 1;
+                // the Q tile of item n - 2 doubled as its O staging tile: wait until its store has read it
+                if (n >= 2 && !mbar_wait(bar(BAR_QFREE + q), ((n >> 1) - 1) & 1, ctl, W + 12)) break;
+                mbar_arrive_expect_tx(bar(BAR_QFULL + q), L::kQBytes);
+                for (int c = 0; c < L::kChunks; ++c)
+                    tma_load_4d(sQ + q * L::kQBytes + c * (kBT * 128), &tmQ, bar(BAR_QFULL + q), c * 64, w.t0, w.h, w.b);
+                // [K;U] of block j, then V of block j-2: V is consumed about two blocks later than K and U of
+                // the same block, so with this lag the producer never waits on the V ring while a [K;U]
+                // stage is free.
+                for (int j = 0; j < w.nblk + 2; ++j) {
+                    if (j < w.nblk) {
+                        if (!mbar_wait(bar(BAR_KUEMPTY + pk.slot), pk.lap ^ 1, ctl, W + 1)) { ok = false; break; }
+                        const uint32_t fku = bar(BAR_KUFULL + pk.slot), dku = sKU + pk.slot * L::kKUStage;
+                        mbar_arrive_expect_tx(fku, L::kKUStage);
 #pragma unroll
-                    for (int c = 0; c < L::kChunks; ++c) {
-                        tma_load_3d(dku + c * 2 * L::kWChunk, &tmK, fku, c * 64, (j0 + j) * kBI, hk);
-                        tma_load_3d(dku + c * 2 * L::kWChunk + L::kWChunk, &tmU, fku, c * 64, (j0 + j) * kBI, hk);
+                        for (int c = 0; c < L::kChunks; ++c) {
+                            tma_load_3d(dku + c * 2 * L::kWChunk, &tmK, fku, c * 64, (w.j0 + j) * kBI, hk);
+                            tma_load_3d(dku + c * 2 * L::kWChunk + L::kWChunk, &tmU, fku, c * 64, (w.j0 + j) * kBI, hk);
+                        }
+                        pk.advance(1);
                     }
-                    pk.advance(1);
-                }
-                if (j >= 2) {
-                    if (!mbar_wait(bar(BAR_VEMPTY + pv.slot), pv.lap ^ 1, ctl, W + 2)) break;
-                    const uint32_t fv = bar(BAR_VFULL + pv.slot), dv = sV + pv.slot * L::kVStage;
-                    mbar_arrive_expect_tx(fv, L::kVStage);
+                    if (j >= 2) {
+                        if (!mbar_wait(bar(BAR_VEMPTY + pv.slot), pv.lap ^ 1, ctl, W + 2)) { ok = false; break; }
+                        const uint32_t fv = bar(BAR_VFULL + pv.slot), dv = sV + pv.slot * L::kVStage;
+                        mbar_arrive_expect_tx(fv, L::kVStage);
 #pragma unroll
-                    for (int c = 0; c < L::kChunks; ++c)
-                        tma_load_3d(dv + c * L::kWChunk, &tmV, fv, c * 64, (j0 + j - 2) * kBI, hk);
-                    pv.advance(1);
+                        for (int c = 0; c < L::kChunks; ++c)
+                            tma_load_3d(dv + c * L::kWChunk, &tmV, fv, c * 64, (w.j0 + j - 2) * kBI, hk);
+                        pv.advance(1);
+                    }
                 }
             }
         }
     } else if (warp == 1 || warp == 2) {
         // ------------------------------------------------------------------ MMA issuers for S = Q [K;U]^T
-        // Two threads (warp 1: even blocks into S buffer 0, warp 2: odd blocks into buffer 1): while one is between
-        // batches -- barrier polls, commits -- the other keeps the tensor pipe fed.  Q is read from tensor memory.
-        // One thread issues a chain, so its instruction stream is kept minimal: descriptors are built once and
-        // advanced by adding constants (the address field counts 16-byte units).
+        // Two threads (warp 1: even blocks into S buffer 0, warp 2: odd blocks into buffer 1; blocks counted through all
+        // work items of the CTA): while one is between batches -- barrier polls, commits -- the other keeps the tensor
+        // pipe fed.  Q is read from tensor memory.  One thread issues a chain, so its instruction stream is kept
+        // minimal: descriptors are built once and advanced by adding constants (the address field counts 16-byte units).
         if (lane == 0) {
             constexpr uint32_t idesc1 = umma_idesc(128, 2 * kBI, false, false);
             const uint64_t dKU0 = desc_kmajor(sKU);
             constexpr uint64_t kKUStep = L::kKUStage >> 4;
             const int sb = warp - 1;
             const uint32_t tS = tmem + kColS0 + sb * kColSStride, tQ = tmem + kColQ;
-            bool ok = mbar_wait(bar(BAR_QT), 0, ctl, W + 3);
-            RingPos<kRing> pw;   // [K;U] stage of block j
-            pw.advance(sb);
-            for (int j = sb; ok && j < nblk; j += 2) {
-                if (!mbar_wait(bar(BAR_KUFULL + pw.slot), pw.lap, ctl, W + 4)) break;
-                // the buffer's previous block (j - 2) is in the activation warps' registers
-                if (j >= 2 && !mbar_wait(bar(BAR_SEMPTY + sb), ((j >> 1) - 1) & 1, ctl, W + 5)) break;
-                tc_fence_after();
-                const uint64_t dku = dKU0 + pw.slot * kKUStep;
+            bool ok = true;
+            int g0 = 0, n = 0;   // blocks before this work item; work items so far
+            for (int item = blockIdx.x; ok && item < args.n_items; item += gridDim.x, ++n) {
+                const FwdItem w = fwd_item(args, item, nblk_total);
+                if (!mbar_wait(bar(BAR_QT), n & 1, ctl, W + 3)) break;   // this item's Q is in tensor memory
+                for (int j = (g0 + sb) & 1; j < w.nblk; j += 2) {
+                    const int g = g0 + j;                                 // g % 2 == sb
+                    const int slot = g % kKURing;
+                    if (!mbar_wait(bar(BAR_KUFULL + slot), (g / kKURing) & 1, ctl, W + 4)) { ok = false; break; }
+                    // the buffer's previous block (g - 2) is in the activation warps' registers
+                    if (g >= 2 && !mbar_wait(bar(BAR_SEMPTY + sb), ((g >> 1) - 1) & 1, ctl, W + 5)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t dku = dKU0 + slot * kKUStep;
 #pragma unroll
-                for (int k = 0; k < DH / 16; ++k) {
-                    const int c = k >> 2, kk = k & 3;
-                    umma_ts(tS, tQ + k * 8, dku + ((c * 2 * L::kWChunk + kk * 32) >> 4), idesc1, k > 0 ? 1u : 0u);
+                    for (int k = 0; k < DH / 16; ++k) {
+                        const int c = k >> 2, kk = k & 3;
+                        umma_ts(tS, tQ + k * 8, dku + ((c * 2 * L::kWChunk + kk * 32) >> 4), idesc1, k > 0 ? 1u : 0u);
+                    }
+                    umma_commit(bar(BAR_KUEMPTY + slot));
+                    umma_commit(bar(BAR_SFULL + sb));
                 }
-                umma_commit(bar(BAR_KUEMPTY + pw.slot));
-                umma_commit(bar(BAR_SFULL + sb));
-                pw.advance(2);
+                g0 += w.nblk;
             }
         }
     } else if (warp == 3) {
         // ------------------------------------------------------------------ MMA issuer 2: O += A V
-        // A comes from tensor memory (slot block % 2), V from shared memory as an MN-major operand.
+        // A comes from tensor memory (slot g % 2), V from shared memory as an MN-major operand.
         if (lane == 0) {
             constexpr uint32_t idesc2 = umma_idesc(128, DH, false, true);
             const uint64_t dV0 = desc_mnmajor(sV, L::kWChunk);
             constexpr uint64_t kVStep = L::kVStage >> 4;
-            RingPos<kRing> pw;
             bool ok = true;
-            for (int j = 0; j < nblk; ++j) {
-                const int slot = j & 1;
-                if (!mbar_wait(bar(BAR_VFULL + pw.slot), pw.lap, ctl, W + 6)) { ok = false; break; }
-                if (!mbar_wait(bar(BAR_AFULL + slot), (j >> 1) & 1, ctl, W + 7)) { ok = false; break; }
-                tc_fence_after();
-                const uint64_t dv = dV0 + pw.slot * kVStep;
-                const uint32_t tA = tmem + kColA0 + slot * kColAStride;
+            int g0 = 0, n = 0;
+            for (int item = blockIdx.x; ok && item < args.n_items; item += gridDim.x, ++n) {
+                const FwdItem w = fwd_item(args, item, nblk_total);
+                // the accumulator of the previous work item has been read out
+                if (n >= 1 && !mbar_wait(bar(BAR_OFREE), (n - 1) & 1, ctl, W + 13)) break;
+                for (int j = 0; j < w.nblk; ++j) {
+                    const int g = g0 + j, slot = g & 1, vs = g % kVRing;
+                    if (!mbar_wait(bar(BAR_VFULL + vs), (g / kVRing) & 1, ctl, W + 6)) { ok = false; break; }
+                    if (!mbar_wait(bar(BAR_AFULL + slot), (g >> 1) & 1, ctl, W + 7)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t dv = dV0 + vs * kVStep;
+                    const uint32_t tA = tmem + kColA0 + slot * kColAStride;
 #pragma unroll
-                for (int k = 0; k < kBI / 16; ++k)
-                    umma_ts(tmem + kColO, tA + k * 8, dv + k * 128, idesc2, (j > 0 || k > 0) ? 1u : 0u);
-                umma_commit(bar(BAR_VEMPTY + pw.slot));
-                umma_commit(bar(BAR_AFREE + slot));
-                pw.advance(1);
+                    for (int k = 0; k < kBI / 16; ++k)
+                        umma_ts(tmem + kColO, tA + k * 8, dv + k * 128, idesc2, (j > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(bar(BAR_VEMPTY + vs));
+                    umma_commit(bar(BAR_AFREE + slot));
+                }
+                if (ok) umma_commit(bar(BAR_OFULL));
+                g0 += w.nblk;
             }
-            if (ok) umma_commit(bar(BAR_OFULL));
         }
     } else if (warp >= 4) {
         // ------------------------------------------------------------------ activation + epilogue
         const int quarter = warp & 3, team = (warp - 4) >> 3, group = ((warp - 4) >> 2) & 1;  // group = column half
         const int row = quarter * 32 + lane;
-        const int t = t0 + row;
-        const bool in_range = t < args.S;
-        const float *rrow = args.R + (long long)b * args.r_sb + (long long)h * args.r_sh + (long long)t * args.r_ss;
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-        bool ok = true;
         const f32x2 half_s0 = f2_pack(args.half_s0, args.half_s0);
-        // Q: shared -> tensor memory, once, by team 0 (thread = token row; its lower four warps copy columns [0, 64)
-        // of d_h, the upper four [64, 128)).
-        if (team == 0) {
-            if (!mbar_wait(bar(BAR_Q), 0, ctl, W + 11)) ok = false;
-            if (ok && group * 64 < DH) {
+        bool ok = true;
+        int g0 = 0, n = 0;   // blocks before this work item; work items so far
+        // Copy of a work item's Q tile from shared into tensor memory, by team 0 (thread = token row; its lower four warps
+        // copy columns [0, 64) of d_h, the upper four [64, 128)).  Done as soon as the previous item's last S has been
+        // read, i.e. before that item's epilogue, so that the first S of the new item is computed under the epilogue.
+        auto copy_q = [&](int nn) -> bool {
+            if (!mbar_wait(bar(BAR_QFULL + (nn & 1)), (nn >> 1) & 1, ctl, W + 11)) return false;
+            if (group * 64 < DH) {
                 uint32_t qv[32];
+                const uint8_t *src = gbase + L::kOffQ + (nn & 1) * L::kQBytes + group * (kBT * 128);
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    const uint4 v = *reinterpret_cast<const uint4 *>(gbase + L::kOffQ + group * (kBT * 128) + sw128_offset(row, c));
+                    const uint4 v = *reinterpret_cast<const uint4 *>(src + sw128_offset(row, c));
                     qv[4 * c] = v.x; qv[4 * c + 1] = v.y; qv[4 * c + 2] = v.z; qv[4 * c + 3] = v.w;
                 }
                 tmem_st32(lane_base + kColQ + group * 32, qv);
@@ -271,91 +317,105 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
             }
             tc_fence_before();
             warp_arrive(bar(BAR_QT));
-        }
-        // sub-network of this team's current block and position inside it; the routing weight is fetched one ahead
-        int e = (j0 + team) / blocks_per_e, in_e = (j0 + team) - e * blocks_per_e;
-        float r_cur = (in_range && e < args.E) ? __ldg(rrow + e) : 0.f;
-        float r_next = (in_range && e + 1 < args.E) ? __ldg(rrow + e + 1) : 0.f;
-        for (int j = team; ok && j < nblk; j += kTeams) {
-            const int sb = j & 1;   // S buffer and A slot of this block
-            const float hr = 0.5f * args.c * r_cur;
-            const f32x2 half_r = f2_pack(hr, hr);
-            if (!mbar_wait(bar(BAR_SFULL + sb), (j >> 1) & 1, ctl, W + 8)) { ok = false; break; }
-            tc_fence_after();
-            const uint32_t ts = lane_base + kColS0 + sb * kColSStride + group * 32;
-            uint32_t m[32], n[32], a[16];  // this thread's 32 columns of M and of N; 32 bf16 of A
-            tmem_ld32x2_sync(ts, ts + kBI, m, n);
-            tc_fence_before();
-            warp_arrive(bar(BAR_SEMPTY + sb));  // S is in registers: the buffer may take block j + 2
+            return true;
+        };
+        if (team == 0 && blockIdx.x < args.n_items) ok = copy_q(0);
+        for (int item = blockIdx.x; ok && item < args.n_items; item += gridDim.x, ++n) {
+            const FwdItem w = fwd_item(args, item, nblk_total);
+            const int t = w.t0 + row;
+            const bool in_range = t < args.S;
+            const float *rrow = args.R + (long long)w.b * args.r_sb + (long long)w.h * args.r_sh + (long long)t * args.r_ss;
+            // this team's first block of the item, its sub-network and position inside it; routing weight fetched one ahead
+            const int jfirst = kTeams == 1 ? 0 : ((g0 + team) & 1);
+            int e = (w.j0 + jfirst) / blocks_per_e, in_e = (w.j0 + jfirst) - e * blocks_per_e;
+            float r_cur = (in_range && e < args.E) ? __ldg(rrow + e) : 0.f;
+            float r_next = (in_range && e + 1 < args.E) ? __ldg(rrow + e + 1) : 0.f;
+            for (int j = jfirst; j < w.nblk; j += kTeams) {
+                const int g = g0 + j, sb = g & 1;   // S buffer and A slot of this block
+                const float hr = 0.5f * args.c * r_cur;
+                const f32x2 half_r = f2_pack(hr, hr);
+                if (!mbar_wait(bar(BAR_SFULL + sb), (g >> 1) & 1, ctl, W + 8)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t ts = lane_base + kColS0 + sb * kColSStride + group * 32;
+                uint32_t m[32], nn[32], a[16];  // this thread's 32 columns of M and of N; 32 bf16 of A
+                tmem_ld32x2_sync(ts, ts + kBI, m, nn);
+                tc_fence_before();
+                warp_arrive(bar(BAR_SEMPTY + sb));  // S is in registers: the buffer may take block g + 2
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-                a[i] = fwd_act_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]), f2_pack_bits(n[2 * i], n[2 * i + 1]), half_r,
-                                    half_s0);
-            // the slot's previous block (j - 2) has been consumed by its O update
-            if (j >= 2 && !mbar_wait(bar(BAR_AFREE + sb), ((j >> 1) - 1) & 1, ctl, W + 9)) { ok = false; break; }
-            tc_fence_after();
-            tmem_st16(lane_base + kColA0 + sb * kColAStride + group * 16, a);
-            tmem_st_wait();
-            tc_fence_before();
-            warp_arrive(bar(BAR_AFULL + sb));
+                for (int i = 0; i < 16; ++i)
+                    a[i] = fwd_act_pair(f2_pack_bits(m[2 * i], m[2 * i + 1]), f2_pack_bits(nn[2 * i], nn[2 * i + 1]), half_r,
+                                        half_s0);
+                // the slot's previous block (g - 2) has been consumed by its O update
+                if (g >= 2 && !mbar_wait(bar(BAR_AFREE + sb), ((g >> 1) - 1) & 1, ctl, W + 9)) { ok = false; break; }
+                tc_fence_after();
+                tmem_st16(lane_base + kColA0 + sb * kColAStride + group * 16, a);
+                tmem_st_wait();
+                tc_fence_before();
+                warp_arrive(bar(BAR_AFULL + sb));
 #pragma unroll
-            for (int k = 0; k < kTeams; ++k)
-                if (++in_e == blocks_per_e) {
-                    in_e = 0;
-                    ++e;
-                    r_cur = r_next;
-                    r_next = (in_range && e + 1 < args.E) ? __ldg(rrow + e + 1) : 0.f;
-                }
-        }
-        if (team != 0) ok = false;   // the epilogue is team 0's
-        // epilogue: O (fp32, tensor memory) -> bf16 -> shared (over the Q tile) -> TMA store
-        if (ok) ok = mbar_wait(bar(BAR_OFULL), 0, ctl, W + 10);
-        if (ok && args.nsplit > 1) {
-            // partial O of this CTA's blocks, fp32, straight from tensor memory to the workspace
-            tc_fence_after();
-            constexpr int kColsPerGroup = DH / 2;
-            const int c0 = group * kColsPerGroup;
-            float *dst = args.part + ((((long long)isplit * gridDim.z + b) * args.H + h) * args.S + t) * DH + c0;
-#pragma unroll
-            for (int g = 0; g < kColsPerGroup / 16; ++g) {
-                uint32_t o[16];
-                tmem_ld16_sync(lane_base + kColO + c0 + g * 16, o);
-                if (in_range) {
-#pragma unroll
-                    for (int v = 0; v < 4; ++v)
-                        *reinterpret_cast<float4 *>(dst + g * 16 + v * 4) =
-                            make_float4(__uint_as_float(o[4 * v]), __uint_as_float(o[4 * v + 1]),
-                                        __uint_as_float(o[4 * v + 2]), __uint_as_float(o[4 * v + 3]));
-                }
+                for (int k = 0; k < kTeams; ++k)
+                    if (++in_e == blocks_per_e) {
+                        in_e = 0;
+                        ++e;
+                        r_cur = r_next;
+                        r_next = (in_range && e + 1 < args.E) ? __ldg(rrow + e + 1) : 0.f;
+                    }
             }
-            tc_fence_before();
-        } else if (ok) {
+            g0 += w.nblk;
+            if (!ok || team != 0) continue;   // the rest of the item is team 0's
+            // every S of this item has been read: the next item's Q may replace it in tensor memory
+            if (item + (int)gridDim.x < args.n_items && !copy_q(n + 1)) { ok = false; break; }
+            // epilogue: O (fp32, tensor memory) -> bf16 -> shared (over this item's Q tile) -> TMA store
+            if (!mbar_wait(bar(BAR_OFULL), n & 1, ctl, W + 10)) { ok = false; break; }
             tc_fence_after();
             constexpr int kColsPerGroup = DH / 2;  // 64, 48 or 32 columns per thread
             const int c0 = group * kColsPerGroup;
+            const uint32_t sO = sQ + (n & 1) * L::kQBytes;
+            if (args.nsplit > 1) {
+                // partial O of this item's blocks, fp32, straight from tensor memory to the workspace
+                float *dst = args.part + ((((long long)w.isplit * args.B + w.b) * args.H + w.h) * args.S + t) * DH + c0;
 #pragma unroll
-            for (int g = 0; g < kColsPerGroup / 16; ++g) {
-                uint32_t o[16];
-                tmem_ld16_sync(lane_base + kColO + c0 + g * 16, o);
+                for (int gg = 0; gg < kColsPerGroup / 16; ++gg) {
+                    uint32_t o[16];
+                    tmem_ld16_sync(lane_base + kColO + c0 + gg * 16, o);
+                    if (in_range) {
 #pragma unroll
-                for (int v = 0; v < 2; ++v) {
-                    const int col = c0 + g * 16 + v * 8;  // first of 8 columns -> one 16-byte chunk
-                    const uint32_t dst = sQ + (col >> 6) * (kBT * 128) + sw128_offset(row, (col & 63) >> 3);
-                    st_shared_v4(dst, pack_bf16(__uint_as_float(o[8 * v + 0]), __uint_as_float(o[8 * v + 1])),
-                                 pack_bf16(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3])),
-                                 pack_bf16(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5])),
-                                 pack_bf16(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7])));
+                        for (int v = 0; v < 4; ++v)
+                            *reinterpret_cast<float4 *>(dst + gg * 16 + v * 4) =
+                                make_float4(__uint_as_float(o[4 * v]), __uint_as_float(o[4 * v + 1]),
+                                            __uint_as_float(o[4 * v + 2]), __uint_as_float(o[4 * v + 3]));
+                    }
+                }
+                tc_fence_before();
+                warp_arrive(bar(BAR_OFREE));
+            } else {
+#pragma unroll
+                for (int gg = 0; gg < kColsPerGroup / 16; ++gg) {
+                    uint32_t o[16];
+                    tmem_ld16_sync(lane_base + kColO + c0 + gg * 16, o);
+#pragma unroll
+                    for (int v = 0; v < 2; ++v) {
+                        const int col = c0 + gg * 16 + v * 8;  // first of 8 columns -> one 16-byte chunk
+                        const uint32_t dst = sO + (col >> 6) * (kBT * 128) + sw128_offset(row, (col & 63) >> 3);
+                        st_shared_v4(dst, pack_bf16(__uint_as_float(o[8 * v + 0]), __uint_as_float(o[8 * v + 1])),
+                                     pack_bf16(__uint_as_float(o[8 * v + 2]), __uint_as_float(o[8 * v + 3])),
+                                     pack_bf16(__uint_as_float(o[8 * v + 4]), __uint_as_float(o[8 * v + 5])),
+                                     pack_bf16(__uint_as_float(o[8 * v + 6]), __uint_as_float(o[8 * v + 7])));
+                    }
+                }
+                tc_fence_before();
+                warp_arrive(bar(BAR_OFREE));   // the accumulator is in registers / shared memory: the next item may overwrite it
+                fence_async_smem();
+                named_bar_sync(1, kTeamThreads);
+                if (warp == 4 && lane == 0) {
+                    for (int c = 0; c < L::kChunks; ++c) tma_store_4d(&tmO, sO + c * (kBT * 128), c * 64, w.t0, w.h, w.b);
+                    tma_store_commit();
+                    tma_store_wait_read();          // the tile has been read: it may take the Q of the item after next
+                    mbar_arrive(bar(BAR_QFREE + (n & 1)));
                 }
             }
-            tc_fence_before();
-            fence_async_smem();
         }
-        if (team == 0) named_bar_sync(1, kTeamThreads);
-        if (ok && args.nsplit == 1 && warp == 4 && lane == 0 && !*abort_flag) {
-            for (int c = 0; c < L::kChunks; ++c) tma_store_4d(&tmO, sQ + c * (kBT * 128), c * 64, t0, h, b);
-            tma_store_commit();
-            tma_store_wait_all();
-        }
+        if (warp == 4 && lane == 0) tma_store_wait_all();
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -451,9 +511,14 @@ int launch_fwd(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
     }
     FwdArgs a{static_cast<const float *>(p.R.ptr), p.R.stride[0], p.R.stride[1], p.R.stride[2],
               p.d.S, p.d.E, p.d.De, p.d.H / p.d.Hkuv, pl.nsplit, pl.blocks_per_split,
-              static_cast<float *>(p.workspace), p.d.H, 0.5f * p.scale.head_scaling,
+              static_cast<float *>(p.workspace), p.d.H, p.d.B, 0, 0, 0.5f * p.scale.head_scaling,
               p.scale.head_scaling * p.scale.up_scaling * p.scale.final_scaling, wait_args(dc)};
-    dim3 grid(((p.d.S + kBT - 1) / kBT) * pl.nsplit, p.d.H, p.d.B);
+    a.tiles_per_seq = (p.d.S + kBT - 1) / kBT;
+    const long long items = (long long)a.tiles_per_seq * p.d.H * p.d.B * pl.nsplit;
+    if (items > 0x7fffffffLL) return FLASHMHF_ERR_BAD_SHAPE;
+    a.n_items = (int)items;
+    // one CTA per SM walks the work items round-robin: the next item's Q load, Q copy and first S overlap this item's epilogue
+    dim3 grid((unsigned)(items < dc->num_sms ? items : dc->num_sms));
     prof_mark(st, kMarkStart);
     fwd_kernel<DH><<<grid, threads_for(DH), L::kTotal, st>>>(tmQ, tmK, tmU, tmV, tmO, a);
     prof_mark(st, kMarkFwd);

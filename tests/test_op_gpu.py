@@ -265,3 +265,27 @@ def test_two_host_threads_on_their_own_streams():
     for i in range(2):
         for a, b in zip(got[i], want[i]):
             assert torch.equal(a, b)
+
+
+def test_decode_calls_with_weights_streamed_from_hbm():
+    """Batched decode of the 1.3B layer with the weights of eight layers cycled (8 x 69 MB: far more than L2), so that
+    every call's weight tiles arrive from HBM, late and out of step with the consumers -- the timing in which a barrier
+    phase mistaken for an older one would show.  Every call must repeat bit for bit and match the oracle."""
+    import flashmhf_b200 as fm
+    B, H, dh, E, de = 64, 16, 128, 22, 256
+    Q, K, U, V, R = orc.make_op_inputs(B, H, 1, dh, E, de, seed=23, dtype=torch.bfloat16, with_dO=False)
+    Qd, Rd = Q.cuda(), R.cuda()
+    g = torch.Generator(device="cuda").manual_seed(24)
+    sets = [[K.cuda(), U.cuda(), V.cuda()]] + [
+        [torch.randn(H, E, de, dh, device="cuda", generator=g).mul(0.02).bfloat16() for _ in range(3)] for _ in range(7)]
+    first = [fm.forward_raw(Qd, *w, Rd) for w in sets]
+    for _ in range(3):
+        again = [fm.forward_raw(Qd, *w, Rd) for w in sets]
+    torch.cuda.synchronize()
+    for a, b in zip(first, again):
+        assert torch.equal(a, b)
+    ref = orc.mhffn_forward(Q.float(), K.float(), U.float(), V.float(), R)
+    assert orc.rel_l2(first[0].cpu().float(), ref) < TOL_BF16
+    for w, o in zip(sets[1:3], first[1:3]):
+        ref = orc.mhffn_forward(Q.float(), *(t.cpu().float() for t in w), R)
+        assert orc.rel_l2(o.cpu().float(), ref) < TOL_BF16
