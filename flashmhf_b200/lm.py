@@ -195,42 +195,6 @@ class _Body(nn.Module):
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
 
 
-HEAD_LOSS_CHUNK = 4096   # token rows per piece of the fused head + loss below
-
-
-class _HeadLoss(torch.autograd.Function):
-    """Mean next-token cross entropy of ``h @ W^T`` without keeping the logits: the rows are walked in pieces of
-    HEAD_LOSS_CHUNK tokens; for each piece the logits (bf16 GEMM), their fp32 log-sum-exp, the loss terms and -- in the
-    same pass -- the gradient of the logits are formed, and the piece's contributions to dh and dW are accumulated at
-    once, so neither the [tokens, vocab] logits nor their fp32 copy (6.6 GB at 16 x 2048 tokens and 50 280 words) ever
-    exist in full.  Same arithmetic as ``F.cross_entropy(logits.float(), labels)`` on bf16 logits, with dW summed over
-    the pieces in bf16.  Used for large CUDA bf16 batches; small ones take the plain expression."""
-
-    @staticmethod
-    def forward(ctx, h, W, labels):
-        n = h.shape[0]
-        dh = torch.empty_like(h)
-        dW = torch.zeros_like(W)
-        total = torch.zeros((), dtype=torch.float32, device=h.device)
-        for a in range(0, n, HEAD_LOSS_CHUNK):
-            b = min(n, a + HEAD_LOSS_CHUNK)
-            logits = (h[a:b] @ W.t()).float()
-            lse = torch.logsumexp(logits, dim=-1, keepdim=True)
-            total += (lse.squeeze(1) - logits.gather(1, labels[a:b, None]).squeeze(1)).sum()
-            logits.sub_(lse).exp_()                                   # softmax
-            logits.scatter_add_(1, labels[a:b, None], torch.full((b - a, 1), -1.0, device=h.device))
-            g = logits.mul_(1.0 / n).to(h.dtype)                      # d loss / d logits of this piece
-            torch.mm(g, W, out=dh[a:b])
-            dW.addmm_(g.t(), h[a:b])
-        ctx.save_for_backward(dh, dW)
-        return total / n
-
-    @staticmethod
-    def backward(ctx, grad):
-        dh, dW = ctx.saved_tensors
-        return dh * grad.to(dh.dtype), dW * grad.to(dW.dtype), None
-
-
 class DecoderLM(nn.Module):
     """ids [B,S] -> logits [B,S,vocab]; ``loss`` is the next-token cross entropy the reference trains with
     (labels = ids shifted by one, mean over B*(S-1) positions, computed in fp32)."""
@@ -269,13 +233,9 @@ class DecoderLM(nn.Module):
         return self.lm_head(self.hidden(ids))
 
     def loss(self, ids):
-        h = self.hidden(ids)[:, :-1]                              # the last position has no label
-        labels = ids[:, 1:].reshape(-1)
-        if h.is_cuda and h.dtype == torch.bfloat16 and h.shape[0] * h.shape[1] >= 4 * HEAD_LOSS_CHUNK:
-            return _HeadLoss.apply(h.reshape(-1, h.shape[-1]), self.lm_head.weight, labels)
-        logits = self.lm_head(h)
+        logits = self.lm_head(self.hidden(ids)[:, :-1])          # the last position has no label
         V = logits.shape[-1]
-        return F.cross_entropy(logits.float().reshape(-1, V), labels)
+        return F.cross_entropy(logits.float().reshape(-1, V), ids[:, 1:].reshape(-1))
 
 
 def train_step(model, opt, ids, reducer=None):
