@@ -343,40 +343,67 @@ def lm_inference(name, cfg, rows, seq, what, args, rank, world, dev, sync_all):
     ids_host = ids_all[a:b].contiguous().pin_memory() if b > a else None
     out_host = torch.zeros(max(1, b - a), dtype=torch.int64).pin_memory()
 
+    ids_dev = ids_host.to(dev) if ids_host is not None else None   # static device buffer the captured graph reads
+
     @torch.no_grad()
+    def forward():
+        if what == "logits":
+            last = model(ids_dev)[:, -1]
+        else:
+            last = model.lm_head(model.hidden(ids_dev)[:, -1])
+        return last.float().argmax(-1)
+
+    # The forward pass of a small model is hundreds of short kernels: replayed from a CUDA graph so that the step is
+    # paced by the GPU and not by the Python interpreter (every kernel of this library only enqueues work and captures).
+    graph, result, ffn_ms = None, None, 0.0
+    if ids_host is not None:
+        for _ in range(2):
+            result = forward()
+        torch.cuda.synchronize()
+        _lib.profile_begin(16 * cfg.num_hidden_layers + 16)     # this library's kernels in one (eager) forward pass
+        result = forward()
+        ffn_ms = sum(sum(v) for v in _lib.profile_end(capacity=16 * cfg.num_hidden_layers + 16).values())
+        try:
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_):
+                result = forward()
+            graph = g_
+        except Exception as e:   # capture is an optimisation of the harness, not a requirement
+            print(f"bench: {name} inference runs without a CUDA graph ({type(e).__name__}: {e})", file=sys.stderr)
+            torch.cuda.synchronize()
+
     def step():
+        nonlocal result
         if ids_host is None:
             return
-        ids = ids_host.to(dev, non_blocking=True)
-        if what == "logits":
-            last = model(ids)[:, -1]
+        ids_dev.copy_(ids_host, non_blocking=True)
+        if graph is not None:
+            graph.replay()
         else:
-            last = model.lm_head(model.hidden(ids)[:, -1])
-        out_host.copy_(last.float().argmax(-1), non_blocking=True)
+            result = forward()
+        out_host.copy_(result, non_blocking=True)
 
     for _ in range(2):
         step()
     sync_all()
     n = args.infer_steps
-    _lib.profile_begin(16 * cfg.num_hidden_layers * n + 16)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(n):
         step()
     e1.record()
     sync_all()
-    kernel_ms = _lib.profile_end(capacity=16 * cfg.num_hidden_layers * n + 16)
     _lib.device_status()
     mine = e0.elapsed_time(e1) / n
     ms = dp.max_over_ranks(mine, dev)
-    ours = sum(sum(v) for v in kernel_ms.values()) / n
-    share = dp.max_over_ranks(ours / mine if ids_host is not None and mine > 0 else 0.0, dev)
+    share = dp.max_over_ranks(ffn_ms / mine if ids_host is not None and mine > 0 else 0.0, dev)
     del model
     torch.cuda.empty_cache()
     return {"model": name, "pass": "bf16 forward, " + ("logits at every position" if what == "logits" else
                                                         "prefill: hidden states of all tokens, logits of the last"),
             "rows": rows, "seq_len": seq, "tokens_per_s": rows * seq / (ms * 1e-3), "ms_per_step": ms, "steps": n, "warmup": 2,
             "split": f"batch rows over {min(world, rows)} of {world} ranks, no collective in the data path",
+            "cuda_graph": graph is not None,
             "ranks_with_work": min(world, rows), "ffn_kernels_share": share,
             "h2d_bytes_per_step_per_rank": (b - a) * seq * 8, "d2h_bytes_per_step_per_rank": (b - a) * 8}
 
@@ -391,7 +418,7 @@ def main():
     ap.add_argument("--small", action="store_true", help="B=2 instead of 16 (for profiler captures)")
     ap.add_argument("--no-lm", action="store_true", help="skip the LM measurements (370M training step, inference runs)")
     ap.add_argument("--lm-steps", type=int, default=8)
-    ap.add_argument("--infer-steps", type=int, default=5)
+    ap.add_argument("--infer-steps", type=int, default=10)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
