@@ -42,3 +42,30 @@ def test_clock_sampler_parses_nvidia_smi_lines():
     assert r["reasons"] == ["sw_power_cap"] and r["power_w"] == 998.1
     s2 = b.ClockSampler(0)
     assert s2.stop()["sm_mhz"] is None                             # never started: reported as unavailable, not as zero
+
+
+def test_recorded_dram_traffic_is_tied_to_kernel_sources_and_workload(tmp_path, monkeypatch):
+    """roofline.traffic comes from a recorded ncu capture; it is reported only for the kernel sources and workload it was taken
+    from, otherwise None with the reason."""
+    import json
+    b = _bench()
+    w = dict(b.WORKLOAD)
+    rec = {"kernel_source_sha256": b.kernel_source_digest(), "workload": {k: w[k] for k in ("B", "S", "H", "Hkuv", "Dh", "E", "De")},
+           "dram_bytes_per_launch": {"bwd_dw_kernel": 2.0e8}, "command": "ncu ..."}
+    f = tmp_path / "t.json"
+    f.write_text(json.dumps(rec))
+    monkeypatch.setattr(b, "TRAFFIC_FILE", str(f))
+    assert b.recorded_traffic("bwd_dw_kernel", w)[0] == 2.0e8
+    assert b.recorded_traffic("fwd_kernel", w)[0] is None
+    assert b.recorded_traffic("bwd_dw_kernel", dict(w, B=2)) == (None, "recorded capture is of another workload")
+    rec["kernel_source_sha256"] = "0" * 64
+    f.write_text(json.dumps(rec))
+    assert b.recorded_traffic("bwd_dw_kernel", w) == (None, "recorded capture is of older kernel sources")
+    assert b.choose_peak({"burst": 2.0, "sustained": 1.0}, 0.05) == ("burst", 2.0)
+    assert b.choose_peak({"burst": 2.0, "sustained": 1.0}, 2.5) == ("sustained", 1.0)
+
+
+def test_both_arms_print_the_same_config():
+    b = _bench()
+    assert b.workload_config(b.WORKLOAD, 1) == b.workload_config(dict(b.WORKLOAD), 1)
+    assert "tokens_per_s" not in b.workload_config(b.WORKLOAD, 1)     # a description of the workload, no measured values
