@@ -289,7 +289,8 @@ def lm_train_370m(args, rank, world, dev, sync_all):
     from flashmhf_b200 import _lib, dp, lm
     cfg = lm.LMConfig.lm_370m()
     Bt, St = 16, 2048
-    model = lm.DecoderLM(cfg).init_weights(seed=0).to(dev).to(torch.bfloat16)   # same seed -> same weights on every rank
+    with torch.device(dev):                      # built and drawn on the GPU: same seed -> same weights on every rank
+        model = lm.DecoderLM(cfg).to(torch.bfloat16).init_weights(seed=0)
     opt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
     red = dp.GradReducer(buckets=dp.lm_buckets(model)) if world > 1 else None
     ids_host = torch.randint(0, cfg.vocab_size, (Bt, St), generator=torch.Generator().manual_seed(rank)).pin_memory()
@@ -338,7 +339,8 @@ def lm_inference(name, cfg, rows, seq, what, args, rank, world, dev, sync_all):
     a, b = dp.shard_range(rows, rank, world) if rank < min(world, rows) else (0, 0)
     if world > rows:                                   # more ranks than rows: the first `rows` ranks take one row each
         a, b = (rank, rank + 1) if rank < rows else (0, 0)
-    model = lm.DecoderLM(cfg).init_weights(seed=0).to(dev).to(torch.bfloat16)
+    with torch.device(dev):
+        model = lm.DecoderLM(cfg).to(torch.bfloat16).init_weights(seed=0)
     ids_all = torch.randint(0, cfg.vocab_size, (rows, seq), generator=torch.Generator().manual_seed(0))
     ids_host = ids_all[a:b].contiguous().pin_memory() if b > a else None
     out_host = torch.zeros(max(1, b - a), dtype=torch.int64).pin_memory()
