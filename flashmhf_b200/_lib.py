@@ -14,7 +14,7 @@ BWD_INPUTS, BWD_WEIGHTS = 1, 2      # flashmhf_bwd_params.parts
 SELFTEST_CODE = 9901                # status code of flashmhf_selftest_bounded_wait
 STATIC_SCRATCH_BYTES = 72 << 20
 
-EXPORTS = ("flashmhf_abi_version", "flashmhf_forward_workspace_bytes", "flashmhf_strerror", "flashmhf_last_cuda_error", "flashmhf_forward",
+EXPORTS = ("flashmhf_abi_version", "flashmhf_forward_workspace_bytes", "flashmhf_strerror", "flashmhf_last_cuda_error", "flashmhf_forward", "flashmhf_forward_chained",
            "flashmhf_backward_workspace_bytes", "flashmhf_backward", "flashmhf_device_status",
            "flashmhf_launch_count", "flashmhf_profile_begin", "flashmhf_profile_end",
            "flashmhf_backward_static_scratch", "flashmhf_prologue_forward",
@@ -90,6 +90,8 @@ def load():
         lib.flashmhf_last_cuda_error.restype = C.c_char_p
         lib.flashmhf_forward.restype = C.c_int
         lib.flashmhf_forward.argtypes = [C.POINTER(FwdParams), C.c_void_p]
+        lib.flashmhf_forward_chained.restype = C.c_int
+        lib.flashmhf_forward_chained.argtypes = [C.POINTER(FwdParams), C.c_void_p]
         lib.flashmhf_forward_workspace_bytes.restype = C.c_size_t
         lib.flashmhf_forward_workspace_bytes.argtypes = [C.POINTER(Dims)]
         lib.flashmhf_backward_workspace_bytes.restype = C.c_size_t

@@ -153,7 +153,7 @@ const char *flashmhf_last_cuda_error(void) { return tl_cuda_error; }
 
 uint64_t flashmhf_launch_count(void) { return g_launches.load(); }
 
-int flashmhf_forward(const flashmhf_fwd_params *p, void *stream) {
+static int forward_entry(const flashmhf_fwd_params *p, void *stream, bool chained) {
     if (!p) return FLASHMHF_ERR_NULL;
     int rc = check_dims(p->d);
     if (rc) return rc;
@@ -167,17 +167,22 @@ int flashmhf_forward(const flashmhf_fwd_params *p, void *stream) {
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     int n = 0;
     if (p->d.dtype == FLASHMHF_F32_CHECK) {
+        if (chained) return FLASHMHF_ERR_BAD_DTYPE;
         cudaError_t e = simt_forward(*p, st, &n);
         if (e != cudaSuccess) {
             set_cuda_error(e, "check forward launch");
             rc = FLASHMHF_ERR_CUDA;
         }
     } else {
-        rc = tc_forward(*p, st, &n);
+        rc = tc_forward(*p, st, &n, chained);
     }
     g_launches += (uint64_t)n;
     return rc;
 }
+
+int flashmhf_forward(const flashmhf_fwd_params *p, void *stream) { return forward_entry(p, stream, false); }
+
+int flashmhf_forward_chained(const flashmhf_fwd_params *p, void *stream) { return forward_entry(p, stream, true); }
 
 size_t flashmhf_forward_workspace_bytes(const flashmhf_dims *d) {
     if (!d || check_dims(*d) != 0) return 0;

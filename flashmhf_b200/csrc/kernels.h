@@ -43,7 +43,8 @@ cudaError_t simt_backward(const flashmhf_bwd_params &p, cudaStream_t st, int *n_
 
 // ---- bf16 tensor-core kernels (tcgen05 / TMEM / TMA) ---------------------------------------
 // Each returns a flashmhf_status (tensor-map encoding can fail with BAD_STRIDE / CUDA).
-int tc_forward(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch);
+// `chained`: launched so that it may overlap the end of the kernel before it on the stream (see flashmhf_forward_chained)
+int tc_forward(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch, bool chained);
 size_t tc_forward_workspace_bytes(const flashmhf_dims &d);
 int tc_backward(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch);
 size_t tc_backward_workspace_bytes(const flashmhf_dims &d);

@@ -58,26 +58,14 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
                  "r"(bytes)
                  : "memory");
 }
-#ifndef FMHF_WAIT_HINT_NS
-#define FMHF_WAIT_HINT_NS 0
-#endif
-// One try: returns whether the phase with this parity has completed.  With a non-zero suspend-time hint the warp may
-// stay suspended inside the instruction for up to that long while the phase is incomplete, instead of returning to spin.
+// One try: returns whether the phase with this parity has completed.
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
-    if (FMHF_WAIT_HINT_NS > 0) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity), "r"((uint32_t)FMHF_WAIT_HINT_NS)
-            : "memory");
-    } else {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-    }
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
     return ok != 0;
 }
 
@@ -151,6 +139,13 @@ __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Until the stores committed so far have READ their shared-memory source (it may then be overwritten).
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
+// Programmatic dependent launch.  A kernel launched with the stream-serialization attribute may start while the kernel
+// before it on the stream still runs; griddep_wait() returns once that kernel has completed and its writes are visible
+// (no-op for a normal launch).  griddep_launch_dependents() lets the kernel after this one start as soon as every CTA
+// of this one has executed it (or exited).
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -388,23 +383,9 @@ __device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
     return d;
 }
 __device__ __forceinline__ f32x2 f2_tanh(f32x2 v) {
-#if defined(FMHF_EXP_NOTANH)
-    return v;
-#elif defined(FMHF_EXP_TANH_H2)
-    // one MUFU op for both values: f16x2 tanh (11-bit mantissa, the accuracy class of tanh.approx.f32)
-    float a, b;
-    f2_unpack(v, a, b);
-    uint32_t h, t;
-    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h) : "f"(b), "f"(a));
-    asm("tanh.approx.f16x2 %0, %1;" : "=r"(t) : "r"(h));
-    float ta, tb;
-    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %2;\n\tcvt.f32.f16 %0, lo;\n\tcvt.f32.f16 %1, hi;\n\t}" : "=f"(ta), "=f"(tb) : "r"(t));
-    return f2_pack(ta, tb);
-#else
     float a, b;
     f2_unpack(v, a, b);
     return f2_pack(fast_tanh(a), fast_tanh(b));
-#endif
 }
 __device__ __forceinline__ uint32_t f2_to_bf16x2(f32x2 v) {
     float a, b;

@@ -32,6 +32,7 @@
 
 #include "kernels.h"
 #include "tc_common.cuh"
+#include <utility>
 #include "tensormap.cuh"
 
 namespace fmhf {
@@ -95,6 +96,10 @@ struct FwdArgs {
     int tiles_per_seq, n_items;   // work items = tiles_per_seq * H * B * nsplit, dealt round-robin to the CTAs
     float half_s0;  // 0.5 * head_scaling: tanh argument scale, sigmoid(s0 m) = 0.5 + 0.5 tanh(0.5 s0 m)
     float c;        // head_scaling * up_scaling * final_scaling, folded into the routing weight
+    // Chained call: launched with programmatic stream serialization.  The CTA may start, and stream weight tiles,
+    // while the kernel before it on the stream still runs; Q and R are read, and anything written, only after
+    // griddep_wait().
+    int chained;
     WaitArgs wait;
 };
 
@@ -176,6 +181,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const bool dead = *abort_flag != 0;
+    if (args.chained) griddep_launch_dependents();   // every CTA of this launch is running: the next call may start
 
     if (dead) {
         // nothing: fall through to the teardown
@@ -195,9 +201,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
                 const int hk = w.h / args.G, q = n & 1;
                 // the Q tile of item n - 2 doubled as its O staging tile: wait until its store has read it
                 if (n >= 2 && !mbar_wait(bar(BAR_QFREE + q), ((n >> 1) - 1) & 1, ctl, W + 12)) break;
-                mbar_arrive_expect_tx(bar(BAR_QFULL + q), L::kQBytes);
-                for (int c = 0; c < L::kChunks; ++c)
-                    tma_load_4d(sQ + q * L::kQBytes + c * (kBT * 128), &tmQ, bar(BAR_QFULL + q), c * 64, w.t0, w.h, w.b);
+                // (the first Q of a chained call is asked for by the activation warps, once the kernel before this one has
+                // completed: this thread touches only the weights and never waits for that)
+                if (!(args.chained && n == 0)) {
+                    mbar_arrive_expect_tx(bar(BAR_QFULL + q), L::kQBytes);
+                    for (int c = 0; c < L::kChunks; ++c)
+                        tma_load_4d(sQ + q * L::kQBytes + c * (kBT * 128), &tmQ, bar(BAR_QFULL + q), c * 64, w.t0, w.h, w.b);
+                }
                 // [K;U] of block j, then V of block j-2: V is consumed about two blocks later than K and U of
                 // the same block, so with this lag the producer never waits on the V ring while a [K;U]
                 // stage is free.
@@ -299,6 +309,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUte
         const f32x2 half_s0 = f2_pack(args.half_s0, args.half_s0);
         bool ok = true;
         int g0 = 0, n = 0;   // blocks before this work item; work items so far
+        if (args.chained) {
+            griddep_wait();   // these warps read R and write O
+            if (warp == 4 && lane == 0 && blockIdx.x < args.n_items) {   // the first item's Q (q.v. the producer)
+                const FwdItem w = fwd_item(args, blockIdx.x, nblk_total);
+                mbar_arrive_expect_tx(bar(BAR_QFULL), L::kQBytes);
+                for (int c = 0; c < L::kChunks; ++c)
+                    tma_load_4d(sQ + c * (kBT * 128), &tmQ, bar(BAR_QFULL), c * 64, w.t0, w.h, w.b);
+            }
+            __syncwarp();
+        }
         // Copy of a work item's Q tile from shared into tensor memory, by team 0 (thread = token row; its lower four warps
         // copy columns [0, 64) of d_h, the upper four [64, 128)).  Done as soon as the previous item's last S has been
         // read, i.e. before that item's epilogue, so that the first S of the new item is computed under the epilogue.
@@ -441,25 +461,52 @@ struct OReduceArgs {
     __nv_bfloat16 *O;
     long long s_b, s_h, s_s;
     int nsplit, H, S, DH;
+    int chained;   // launched with programmatic stream serialization, between two chained forward kernels
 };
-__global__ void __launch_bounds__(256) o_reduce_kernel(const OReduceArgs a) {
-    const long long n4 = a.plane / 4;
-    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < n4;
-         idx += (long long)gridDim.x * blockDim.x) {
-        const long long el = idx * 4;
-        float4 acc = *reinterpret_cast<const float4 *>(a.part + el);
-        for (int s = 1; s < a.nsplit; ++s) {
-            const float4 v = *reinterpret_cast<const float4 *>(a.part + (long long)s * a.plane + el);
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        }
-        const int c = (int)(el % a.DH);
-        const long long r1 = el / a.DH;
-        const int t = (int)(r1 % a.S);
-        const long long r2 = r1 / a.S;
-        const int h = (int)(r2 % a.H);
-        const long long b = r2 / a.H;
-        *reinterpret_cast<uint2 *>(a.O + b * a.s_b + h * a.s_h + t * a.s_s + c) =
+// 128 threads and few registers: its CTAs fit beside the forward kernel's on an SM, so a chained launch is resident (and
+// has let the next forward launch in turn) long before the forward kernel it waits for ends.
+__global__ void __maxnreg__(48) o_reduce_kernel(const OReduceArgs a) {
+    if (a.chained) {
+        griddep_launch_dependents();
+        griddep_wait();
+    }
+    // Every thread takes two 16-byte pieces of O at a time and has the loads of three splits of both in flight at once
+    // (the partial sums come from L2 while the next call's weights stream in from HBM: latency is what this kernel is
+    // made of); the splits are added in index order.  48 registers: 128 threads of it fit beside the d_h = 128 forward CTA.
+    // (a split call has fewer than SMs / 2 token tiles: every index fits 32 bits)
+    const int n4 = (int)(a.plane / 4), stride = (int)(gridDim.x * blockDim.x);
+    auto store = [&](int idx, const float4 &acc) {
+        const int per_row = a.DH / 4;
+        const int r1 = idx / per_row, c = (idx - r1 * per_row) * 4;
+        const int r2 = r1 / a.S, t = r1 - r2 * a.S;
+        const int b = r2 / a.H, h = r2 - b * a.H;
+        *reinterpret_cast<uint2 *>(a.O + (long long)b * a.s_b + (long long)h * a.s_h + (long long)t * a.s_s + c) =
             make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+    };
+    const float4 *part4 = reinterpret_cast<const float4 *>(a.part);
+    const int plane4 = n4;
+    for (int idx = (int)(blockIdx.x * blockDim.x + threadIdx.x); idx < n4; idx += 2 * stride) {
+        const bool two = idx + stride < n4;
+        const int idx1 = two ? idx + stride : idx;
+        float4 acc0 = __ldcg(part4 + idx), acc1 = __ldcg(part4 + idx1);
+        for (int s0 = 1; s0 < a.nsplit; s0 += 3) {
+            float4 v0[3], v1[3];
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                const float4 *src = part4 + (long long)min(s0 + k, a.nsplit - 1) * plane4;
+                v0[k] = __ldcg(src + idx);
+                v1[k] = __ldcg(src + idx1);
+            }
+#pragma unroll
+            for (int k = 0; k < 3; ++k) {
+                if (s0 + k < a.nsplit) {
+                    acc0.x += v0[k].x; acc0.y += v0[k].y; acc0.z += v0[k].z; acc0.w += v0[k].w;
+                    acc1.x += v1[k].x; acc1.y += v1[k].y; acc1.z += v1[k].z; acc1.w += v1[k].w;
+                }
+            }
+        }
+        store(idx, acc0);
+        if (two) store(idx1, acc1);
     }
 }
 
@@ -482,8 +529,24 @@ FwdPlan fwd_plan(const flashmhf_dims &d, int num_sms) {
     return p;
 }
 
+// Launch with programmatic stream serialization: the kernel may start before the one ahead of it on the stream has ended.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 template <int DH>
-int launch_fwd(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
+int launch_fwd(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch, bool chained) {
     using L = FwdSmem<DH>;
     CUtensorMap tmQ, tmK, tmU, tmV, tmO;
     int rc;
@@ -494,7 +557,7 @@ int launch_fwd(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
     if ((rc = encode_act_map(&tmO, p.O, p.d, kBT)) != 0) return rc;
     const DeviceCtl *dc = device_ctl();
     if (!dc) return FLASHMHF_ERR_CUDA;
-    {  // the attribute is per device and per kernel: set once for each pair
+    {  // the attributes are per device and per kernel: set once for each pair
         static std::atomic<bool> done[64];
         if (!done[dc->device].load(std::memory_order_acquire)) {
             cudaError_t e = cudaFuncSetAttribute(fwd_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::kTotal);
@@ -512,30 +575,39 @@ int launch_fwd(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
     FwdArgs a{static_cast<const float *>(p.R.ptr), p.R.stride[0], p.R.stride[1], p.R.stride[2],
               p.d.S, p.d.E, p.d.De, p.d.H / p.d.Hkuv, pl.nsplit, pl.blocks_per_split,
               static_cast<float *>(p.workspace), p.d.H, p.d.B, 0, 0, 0.5f * p.scale.head_scaling,
-              p.scale.head_scaling * p.scale.up_scaling * p.scale.final_scaling, wait_args(dc)};
+              p.scale.head_scaling * p.scale.up_scaling * p.scale.final_scaling, chained ? 1 : 0, wait_args(dc)};
     a.tiles_per_seq = (p.d.S + kBT - 1) / kBT;
     const long long items = (long long)a.tiles_per_seq * p.d.H * p.d.B * pl.nsplit;
     if (items > 0x7fffffffLL) return FLASHMHF_ERR_BAD_SHAPE;
     a.n_items = (int)items;
     // one CTA per SM walks the work items round-robin: the next item's Q load, Q copy and first S overlap this item's epilogue
-    dim3 grid((unsigned)(items < dc->num_sms ? items : dc->num_sms));
+    // (a split call has one item per CTA: tiles * splits <= SMs)
+    const unsigned grid = (unsigned)(items < dc->num_sms ? items : dc->num_sms);
     prof_mark(st, kMarkStart);
-    fwd_kernel<DH><<<grid, threads_for(DH), L::kTotal, st>>>(tmQ, tmK, tmU, tmV, tmO, a);
+    cudaError_t e;
+    if (chained) {
+        e = launch_chained(fwd_kernel<DH>, dim3(grid), dim3(threads_for(DH)), L::kTotal, st, tmQ, tmK, tmU, tmV, tmO, a);
+    } else {
+        fwd_kernel<DH><<<grid, threads_for(DH), L::kTotal, st>>>(tmQ, tmK, tmU, tmV, tmO, a);
+        e = cudaGetLastError();
+    }
     prof_mark(st, kMarkFwd);
     *n_launch += 1;
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { set_cuda_error(e, "fwd_kernel launch"); return FLASHMHF_ERR_CUDA; }
     if (pl.nsplit > 1) {
         const long long plane = (long long)p.d.B * p.d.H * p.d.S * DH;
         OReduceArgs ra{static_cast<const float *>(p.workspace), plane, static_cast<__nv_bfloat16 *>(p.O.ptr),
-                       p.O.stride[0], p.O.stride[1], p.O.stride[2], pl.nsplit, p.d.H, p.d.S, DH};
+                       p.O.stride[0], p.O.stride[1], p.O.stride[2], pl.nsplit, p.d.H, p.d.S, DH, chained ? 1 : 0};
         const long long n4 = plane / 4;
-        const long long cap = (long long)dc->num_sms * 4;
-        const int blocks = (int)((n4 + 255) / 256 < cap ? (n4 + 255) / 256 : cap);
-        o_reduce_kernel<<<blocks, 256, 0, st>>>(ra);
+        // chained: at most one (small) CTA per SM, so that all of them are resident beside the forward kernel's
+        const long long cap = chained ? (long long)dc->num_sms : (long long)dc->num_sms * 8;
+        const int blocks = (int)((n4 + 127) / 128 < cap ? (n4 + 127) / 128 : cap);
+        if (chained) e = launch_chained(o_reduce_kernel, dim3(blocks), dim3(128), 0, st, ra);
+        else o_reduce_kernel<<<blocks, 128, 0, st>>>(ra);
         prof_mark(st, kMarkFwdReduce);
         *n_launch += 1;
-        if ((e = cudaGetLastError()) != cudaSuccess) { set_cuda_error(e, "o_reduce_kernel launch"); return FLASHMHF_ERR_CUDA; }
+        if (!chained) e = cudaGetLastError();
+        if (e != cudaSuccess) { set_cuda_error(e, "o_reduce_kernel launch"); return FLASHMHF_ERR_CUDA; }
     }
     return FLASHMHF_OK;
 }
@@ -549,11 +621,11 @@ size_t tc_forward_workspace_bytes(const flashmhf_dims &d) {
     return (size_t)pl.nsplit * (size_t)d.B * d.H * d.S * d.Dh * sizeof(float);
 }
 
-int tc_forward(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch) {
+int tc_forward(const flashmhf_fwd_params &p, cudaStream_t st, int *n_launch, bool chained) {
     switch (p.d.Dh) {
-        case 64: return launch_fwd<64>(p, st, n_launch);
-        case 96: return launch_fwd<96>(p, st, n_launch);
-        case 128: return launch_fwd<128>(p, st, n_launch);
+        case 64: return launch_fwd<64>(p, st, n_launch, chained);
+        case 96: return launch_fwd<96>(p, st, n_launch, chained);
+        case 128: return launch_fwd<128>(p, st, n_launch, chained);
         default: return FLASHMHF_ERR_BAD_SHAPE;
     }
 }

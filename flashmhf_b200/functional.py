@@ -6,6 +6,7 @@ twin (kernels/thunderkittens/flash_ffn_moe_torch.py:5-24): it saves the five inp
 intermediate, and recomputes in backward.  PyTorch supplies device memory and the current stream;
 all arithmetic runs in the CUDA library."""
 import ctypes as C
+import threading
 
 import torch
 
@@ -102,13 +103,80 @@ def _tokens_as_sequence(*ts):
     return [t.permute(2, 1, 0, 3) for t in ts]
 
 
-def forward_raw(Q, K, U, V, R, out=None, scaling=_lib.NO_SCALING):
-    """O = flashmhf_forward(...) on the current stream; no autograd."""
-    B, H, S, dh, hk, E, de = _validate(Q, K, U, V, R)
+class _FwdPlan:
+    """What a forward call over tensors of given shapes, strides, dtypes and alignment needs, worked out once: the
+    parameter struct (strides, dims, scaling filled in; the five data pointers are set per call), the scratch size, and
+    whether a decode-shaped call is passed as one sequence."""
+    __slots__ = ("params", "ref", "ws_bytes", "call")
+
+
+class _PlanCache(threading.local):
+    """Per thread (a plan's parameter struct is written into on every call)."""
+
+    def __init__(self):
+        self.plans = {}
+
+
+_fwd_plans = _PlanCache()
+_MAX_PLANS = 256
+
+
+def _fwd_key(Q, K, U, V, R, out, scaling, chained):
+    return (Q.shape, Q.stride(), Q.dtype, Q.device, Q.data_ptr() & 15,
+            K.shape, K.stride(), K.dtype, K.device, K.data_ptr() & 15,
+            U.shape, U.stride(), U.dtype, U.device, U.data_ptr() & 15,
+            V.shape, V.stride(), V.dtype, V.device, V.data_ptr() & 15,
+            R.shape, R.stride(), R.dtype, R.device, R.data_ptr() & 3,
+            None if out is None else (out.shape, out.stride(), out.dtype, out.device, out.data_ptr() & 15),
+            scaling if type(scaling) is tuple else tuple(scaling), chained)
+
+
+def forward_raw(Q, K, U, V, R, out=None, scaling=_lib.NO_SCALING, chained=False, workspace=None):
+    """O = flashmhf_forward(...) on the current stream; no autograd.
+
+    ``chained``: use ``flashmhf_forward_chained`` -- for back-to-back calls over constant weights (a decode loop,
+    usually replayed from a CUDA graph): the call may start, and stream in its first weight tiles, while the kernel
+    before it on the stream still runs.  The caller promises that K, U, V are not written by the operation directly
+    before the call.  Same result, bit for bit.
+    ``workspace``: optional uint8 tensor to use as the call's scratch (at least ``flashmhf_forward_workspace_bytes``).
+
+    The checks and the layout decisions depend only on shapes, strides, dtypes, devices and pointer alignment; they are
+    made once per such combination and remembered (per thread), so that a repeated call costs little more than filling
+    in five pointers -- a decode-shaped call lasts some twenty microseconds on the GPU."""
+    key = _fwd_key(Q, K, U, V, R, out, scaling, chained)
+    plan = _fwd_plans.plans.get(key)
+    if plan is None:
+        return _forward_first(key, Q, K, U, V, R, out, scaling, chained, workspace)
+    O = torch.empty_like(Q) if out is None else out
+    p = plan.params
+    p.Q.ptr, p.K.ptr, p.U.ptr, p.V.ptr, p.R.ptr, p.O.ptr = (Q.data_ptr(), K.data_ptr(), U.data_ptr(), V.data_ptr(),
+                                                            R.data_ptr(), O.data_ptr())
+    ws = None
+    if plan.ws_bytes:
+        ws = _scratch(workspace, plan.ws_bytes, Q.device)
+        p.workspace = ws.data_ptr()
+    with _on_device(Q.device):
+        _lib.check(plan.call(plan.ref, torch.cuda.current_stream().cuda_stream))
+    return O
+
+
+def _scratch(workspace, nbytes, device):
+    if workspace is None:
+        return torch.empty(nbytes, dtype=torch.uint8, device=device)
+    if workspace.device != device or workspace.dtype != torch.uint8 or workspace.numel() < nbytes or \
+            workspace.data_ptr() % 256:
+        raise ValueError(f"workspace must be a 256-byte aligned uint8 tensor of at least {nbytes} bytes on {device}")
+    return workspace
+
+
+def _forward_first(key, Q0, K0, U0, V0, R0, out, scaling, chained, workspace):
+    """The full path: validate, copy what the library cannot address in place, call; remember the plan when the call
+    needed no copy (then the same key always leads to the same parameter struct)."""
+    B, H, S, dh, hk, E, de = _validate(Q0, K0, U0, V0, R0)
     lib = _lib.load()
     sc = _scaling(scaling)
-    Q, K, U, V = _prep(Q), _prep(K, True, de), _prep(U, True, de), _prep(V, True, de)
-    R = _routing(R)
+    Q, K, U, V = _prep(Q0), _prep(K0, True, de), _prep(U0, True, de), _prep(V0, True, de)
+    R = _routing(R0)
     O = torch.empty_like(Q) if out is None else out  # keeps Q's memory layout ([B,H,S,d] or [B,S,H,d])
     Qk, Rk, Ok = Q, R, O
     if S == 1 and B > 1:
@@ -119,11 +187,18 @@ def forward_raw(Q, K, U, V, R, out=None, scaling=_lib.NO_SCALING):
             Qk, Rk, Ok = Q, R, O
     d = _dims(B, H, S, dh, hk, E, de, Q.dtype)
     nbytes = int(lib.flashmhf_forward_workspace_bytes(C.byref(d)))
-    ws = torch.empty(nbytes, dtype=torch.uint8, device=Q.device) if nbytes else None
+    ws = _scratch(workspace, nbytes, Q.device) if nbytes else None
     p = _lib.FwdParams(d, _tensor(Qk), _tensor(K), _tensor(U), _tensor(V), _tensor(Rk), _tensor(Ok),
                        ws.data_ptr() if nbytes else None, nbytes, sc)
+    call = lib.flashmhf_forward_chained if chained else lib.flashmhf_forward
+    ref = C.byref(p)
     with _on_device(Q.device):
-        _lib.check(lib.flashmhf_forward(C.byref(p), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        _lib.check(call(ref, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    in_place = all(a is b for a, b in ((Q, Q0), (K, K0), (U, U0), (V, V0), (R, R0)))
+    if in_place and len(_fwd_plans.plans) < _MAX_PLANS:
+        plan = _FwdPlan()
+        plan.params, plan.ref, plan.ws_bytes, plan.call = p, ref, nbytes, call
+        _fwd_plans.plans[key] = plan
     return O
 
 

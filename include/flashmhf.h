@@ -113,6 +113,17 @@ const char *flashmhf_last_cuda_error(void);
  * kernels/triton/flash_mlp_moe.py:777-790. */
 int flashmhf_forward(const flashmhf_fwd_params *p, void *stream);
 
+/* Forward for back-to-back calls over constant weights (a decode loop: the O of one layer's call becomes, a few small
+ * kernels later, the Q of the next).  Same arguments, same results (bit for bit) as flashmhf_forward; bf16 only.  Its
+ * kernels are launched with programmatic stream serialization: they may become resident while the operation before
+ * them on the stream is still running, and the forward kernel streams K, U, V tiles in meanwhile; Q and R are read, and
+ * O and the workspace written, only after that operation has completed.  Between two such calls the GPU therefore
+ * never waits for a launch, and the second call's first weight tiles are in shared memory when its Q arrives.
+ * The caller promises that K, U and V are not written by the operation directly before this call on the stream.
+ * Capturable in a CUDA graph.  Reference counterpart: the same launches as flashmhf_forward
+ * (flash_ffn_moe.cu:938-1007), which the reference issues in plain stream order. */
+int flashmhf_forward_chained(const flashmhf_fwd_params *p, void *stream);
+
 /* Bytes of scratch flashmhf_forward needs for these dims.  0 unless there are fewer token tiles
  * (ceil(S/128) * H * B) than about half the SMs -- the decode-shaped case (reference: batched decode
  * through the same call, models/flashmhf/modeling_mhffnmoe.py:406-408) -- where the intermediate

@@ -11,6 +11,7 @@ SwiGLU with the same parameter count (W_g, W_u, W_d of shape [I, H*d_h]) has the
 Prints markdown tables.
 """
 import argparse
+import time
 import json
 import os
 import sys
@@ -144,9 +145,11 @@ def lm_runs(args):
 
 def decode_runs(args):
     """Decode-shaped forward calls: B sequences, one new token each.  The weights of 8 layers are cycled so that every
-    call streams its K, U, V from HBM (one layer's weights would stay in L2).  Reported per layer call: time from Python
-    (host launch included), kernel-only time from CUDA events, and the same calls replayed from a CUDA graph; GB/s is
-    the layer's weight bytes over that time (algorithmic bytes of the call: 6*H*E*d_e*d_h, Q/O/R are negligible)."""
+    call streams its K, U, V from HBM (one layer's weights would stay in L2).  Reported per layer call: the time the
+    interpreter needs to issue it, the time from Python (issue and execution overlapped), kernel-only time from CUDA
+    events, the same calls replayed from a CUDA graph, and a chain of the eight layers (each call's O is the next
+    call's Q) through the chained entry point, replayed from a graph; GB/s is the layer's weight bytes over that time
+    (algorithmic bytes of the call: 6*H*E*d_e*d_h, Q/O/R are negligible)."""
     import flashmhf_b200 as fm
     from flashmhf_b200 import _lib
     hbm = 6547.0
@@ -155,8 +158,9 @@ def decode_runs(args):
             hbm = float(json.load(f)["hbm_gbs"])
     except (OSError, KeyError, ValueError):
         pass
-    print(f"| shape | weights MB | python call us | kernels us (fwd + reduce) | fwd kernel GB/s | of measured {hbm:.0f} | graph replay us | graph GB/s |")
-    print("|---|---|---|---|---|---|---|---|")
+    print(f"| shape | weights MB | host us per call | python call us | kernels us (fwd + reduce) | fwd kernel GB/s | of measured {hbm:.0f} | "
+          f"graph replay us | graph GB/s | chained graph us | chained GB/s | of measured {hbm:.0f} |")
+    print("|---|---|---|---|---|---|---|---|---|---|---|---|")
     for (B, H, E, de, dh, name) in [(64, 16, 22, 256, 128, "1.3B layer, 64 tokens"), (8, 16, 22, 256, 128, "1.3B layer, 8 tokens"),
                                     (64, 8, 11, 256, 128, "370M layer, 64 tokens")]:
         g = torch.Generator(device="cuda").manual_seed(0)
@@ -169,8 +173,10 @@ def decode_runs(args):
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
         n = 80
         ev[0].record()
+        t_host = time.perf_counter()
         for i in range(n):
             fm.forward_raw(Q, *Ws[i % 8], R)
+        host_us = (time.perf_counter() - t_host) / n * 1e6   # time the interpreter needs to issue a call
         ev[1].record()
         torch.cuda.synchronize()
         call_us = ev[0].elapsed_time(ev[1]) / n * 1e3
@@ -199,9 +205,37 @@ def decode_runs(args):
         ev[1].record()
         torch.cuda.synchronize()
         graph_us = ev[0].elapsed_time(ev[1]) / 80 * 1e3
-        print(f"| {name} | {wbytes / 1e6:.1f} | {call_us:.1f} | {fwd_us:.1f} + {red_us:.1f} | {wbytes / fwd_us / 1e3:.0f} | "
-              f"{wbytes / fwd_us / 1e3 / hbm:.2f} | {graph_us:.1f} | {wbytes / graph_us / 1e3:.0f} |", flush=True)
-        del outs, gr, Ws
+        # the same eight layers as a chain (each call's O is the next call's Q), with the chained entry point
+        def chain(chained):
+            q = Q
+            for i in range(8):
+                q = fm.forward_raw(q, *Ws[i], R, chained=chained)
+            return q
+        want = chain(False)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            got = chain(True)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        same = torch.equal(want, got)
+        gc = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gc):
+            got = chain(True)
+        gc.replay()
+        torch.cuda.synchronize()
+        same = same and torch.equal(want, got)
+        ev[0].record()
+        for _ in range(10):
+            gc.replay()
+        ev[1].record()
+        torch.cuda.synchronize()
+        _lib.device_status()
+        chain_us = ev[0].elapsed_time(ev[1]) / 80 * 1e3
+        print(f"| {name} | {wbytes / 1e6:.1f} | {host_us:.1f} | {call_us:.1f} | {fwd_us:.1f} + {red_us:.1f} | {wbytes / fwd_us / 1e3:.0f} | "
+              f"{wbytes / fwd_us / 1e3 / hbm:.2f} | {graph_us:.1f} | {wbytes / graph_us / 1e3:.0f} | "
+              f"{chain_us:.1f}{'' if same else ' (MISMATCH)'} | {wbytes / chain_us / 1e3:.0f} | {wbytes / chain_us / 1e3 / hbm:.2f} |",
+              flush=True)
+        del outs, gr, gc, Ws
 
 
 def main():

@@ -289,3 +289,46 @@ def test_decode_calls_with_weights_streamed_from_hbm():
     for w, o in zip(sets[1:3], first[1:3]):
         ref = orc.mhffn_forward(Q.float(), *(t.cpu().float() for t in w), R)
         assert orc.rel_l2(o.cpu().float(), ref) < TOL_BF16
+
+
+@pytest.mark.parametrize("B,S,H,dh,E,de", [(64, 1, 16, 128, 22, 256), (8, 1, 16, 128, 22, 256), (3, 1, 4, 64, 2, 64),
+                                           (5, 1, 6, 96, 3, 128), (2, 300, 4, 128, 4, 128)])
+def test_chained_forward_equals_plain_forward(B, S, H, dh, E, de):
+    """`flashmhf_forward_chained` (launch may overlap the end of the kernel before it; split partial sums added inside
+    the kernel) gives the plain call's bits: single calls, a chain of eight layers whose O feeds the next Q, the chain
+    replayed from a CUDA graph, and plain calls in between (the per-tile counters are back at zero after every call)."""
+    import flashmhf_b200 as fm
+    Q, K, U, V, R = orc.make_op_inputs(B, H, S, dh, E, de, seed=31, dtype=torch.bfloat16, with_dO=False)
+    Qd, Rd = Q.cuda(), R.cuda()
+    g = torch.Generator(device="cuda").manual_seed(32)
+    sets = [[K.cuda(), U.cuda(), V.cuda()]] + [
+        [torch.randn(H, E, de, dh, device="cuda", generator=g).mul(0.05).bfloat16() for _ in range(3)] for _ in range(7)]
+    plain = fm.forward_raw(Qd, *sets[0], Rd)
+    ref = orc.mhffn_forward(Q.float(), K.float(), U.float(), V.float(), R)
+    assert orc.rel_l2(plain.cpu().float(), ref) < TOL_BF16
+    for _ in range(3):
+        assert torch.equal(fm.forward_raw(Qd, *sets[0], Rd, chained=True), plain)
+
+    def chain(chained):
+        q = Qd
+        for w in sets:
+            q = fm.forward_raw(q, *w, Rd, chained=chained) * 4.0   # a small kernel between the calls, as a model has
+        return q
+
+    want = chain(False)
+    got = chain(True)
+    assert torch.equal(got, want)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        chain(True)
+    torch.cuda.current_stream().wait_stream(side)
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        out = chain(True)
+    for _ in range(3):
+        gr.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    assert torch.equal(fm.forward_raw(Qd, *sets[0], Rd), plain)
+    fm.check_device_status()
