@@ -13,7 +13,7 @@ The metric is algorithmic TFLOP/s: 18*T*H*I*d_h FLOPs per step (3 forward + 6 gr
 recomputation the backward needs is NOT counted) divided by the step time, summed over GPUs.
 Next to it, in the same JSON line: the same through the public autograd API with host buffers (`e2e`),
 the dominant kernel's roofline fraction, the CPU baseline, a full 370M training step (`train_370m`) and
-two token-sharded inference runs (`infer_128m`, `prefill_1p3b`).  Prints ONE JSON line on rank 0.
+three token-sharded inference runs (`infer_128m`, `prefill_1p3b`, `decode_1p3b`).  Prints ONE JSON line on rank 0.
 """
 import argparse
 import hashlib
@@ -410,6 +410,94 @@ def lm_inference(name, cfg, rows, seq, what, args, rank, world, dev, sync_all):
             "h2d_bytes_per_step_per_rank": (b - a) * seq * 8, "d2h_bytes_per_step_per_rank": (b - a) * 8}
 
 
+def lm_decode(name, cfg, rows, context, args, rank, world, dev, sync_all):
+    """Batched decode: `rows` sequences, each with `context` positions in the key/value cache (synthetic contents), one
+    new token per sequence per step; the sequences are split over the ranks (weights replicated, no collective).  Each
+    timed step copies this rank's token ids from pinned host memory, runs the bf16 step (replayed from a CUDA graph: a
+    decode step is a few hundred short kernels) and reads the arg-max of the logits back.  The step is bound by HBM:
+    it reads every weight matrix once and the cached keys and values of `context` positions; both byte counts and the
+    achieved rate per GPU are reported, and the share of the step spent in this library's kernels."""
+    from flashmhf_b200 import _lib, dp, lm
+    a, b = dp.shard_range(rows, rank, world) if rank < min(world, rows) else (0, 0)
+    if world > rows:
+        a, b = (rank, rank + 1) if rank < rows else (0, 0)
+    n_mine = b - a
+    with torch.device(dev):
+        model = lm.DecoderLM(cfg).to(torch.bfloat16).init_weights(seed=0)
+    weight_bytes = sum(p.numel() * p.element_size() for k, p in model.named_parameters()
+                       if cfg.tie_word_embeddings or not k.startswith("model.embed_tokens"))
+    ids_all = torch.randint(0, cfg.vocab_size, (rows, 1), generator=torch.Generator().manual_seed(0))
+    graph, result, ffn_ms, kv_bytes = None, None, 0.0, 0
+    if n_mine:
+        cache = lm.KVCache(cfg, n_mine, context + 8, dev)
+        g = torch.Generator(device=dev).manual_seed(1 + rank)
+        cache.k.normal_(0.0, 1.0, generator=g)
+        cache.v.normal_(0.0, 1.0, generator=g)
+        kv_bytes = cache.nbytes(context + 1)
+        ids_host = ids_all[a:b].contiguous().pin_memory()
+        ids_dev = ids_host.to(dev)
+        out_host = torch.zeros(n_mine, dtype=torch.int64).pin_memory()
+
+        @torch.no_grad()
+        def forward():
+            return model.decode_step(ids_dev, cache, context).float().argmax(-1)
+
+        for _ in range(2):
+            result = forward()
+        torch.cuda.synchronize()
+        _lib.profile_begin(16 * cfg.num_hidden_layers + 16)
+        result = forward()
+        ffn_ms = sum(sum(v) for v in _lib.profile_end(capacity=16 * cfg.num_hidden_layers + 16).values())
+        try:
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_):
+                result = forward()
+            graph = g_
+        except Exception as e:   # capture is an optimisation of the harness, not a requirement
+            print(f"bench: {name} decode runs without a CUDA graph ({type(e).__name__}: {e})", file=sys.stderr)
+            torch.cuda.synchronize()
+
+    def step():
+        nonlocal result
+        if not n_mine:
+            return
+        ids_dev.copy_(ids_host, non_blocking=True)
+        if graph is not None:
+            graph.replay()
+        else:
+            result = forward()
+        out_host.copy_(result, non_blocking=True)
+
+    for _ in range(3):
+        step()
+    sync_all()
+    n = args.infer_steps
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        step()
+    e1.record()
+    sync_all()
+    _lib.device_status()
+    mine = e0.elapsed_time(e1) / n
+    ms = dp.max_over_ranks(mine, dev)
+    share = dp.max_over_ranks(ffn_ms / mine if n_mine and mine > 0 else 0.0, dev)
+    ffn_max = dp.max_over_ranks(ffn_ms, dev)
+    kv_max = dp.max_over_ranks(float(kv_bytes), dev)
+    if n_mine:
+        del cache
+    del model
+    torch.cuda.empty_cache()
+    return {"model": name, "pass": "bf16 decode step: one new token per sequence, attention over the cached context",
+            "rows": rows, "context": context, "tokens_per_s": rows / (ms * 1e-3), "ms_per_step": ms, "steps": n, "warmup": 3,
+            "split": f"sequences over {min(world, rows)} of {world} ranks, no collective in the data path",
+            "cuda_graph": graph is not None, "ranks_with_work": min(world, rows),
+            "weight_bytes_per_step_per_rank": weight_bytes, "kv_bytes_per_step_per_rank": kv_max,
+            "hbm_gbs_per_rank": (weight_bytes + kv_max) / (ms * 1e-3) / 1e9,
+            "ffn_kernels_ms": ffn_max, "ffn_kernels_share": share,
+            "h2d_bytes_per_step_per_rank": n_mine * 8, "d2h_bytes_per_step_per_rank": n_mine * 8}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -556,7 +644,7 @@ def main():
     value = fl / (ms * 1e-3) / 1e12
     e2e_value = fl / (e2e_ms * 1e-3) / 1e12
 
-    train = infer = prefill = None
+    train = infer = prefill = decode = None
     if not args.no_lm and not args.small:
         from flashmhf_b200 import lm
         del res, outs_host, hQ, hdO, hR, keep, dev_in
@@ -565,6 +653,7 @@ def main():
         torch.cuda.empty_cache()
         infer = lm_inference("128M", lm.LMConfig.lm_128m(), 8, 2048, "logits", args, rank, world, dev, sync_all)
         prefill = lm_inference("1.3B", lm.LMConfig.lm_1p3b(), 4, 8192, "prefill", args, rank, world, dev, sync_all)
+        decode = lm_decode("1.3B", lm.LMConfig.lm_1p3b(), 64, 4096, args, rank, world, dev, sync_all)
 
     if rank == 0:
         peaks = measured_peaks()
@@ -604,6 +693,7 @@ def main():
             out["train_370m"] = train
             out["infer_128m"] = infer
             out["prefill_1p3b"] = prefill
+            out["decode_1p3b"] = decode
         if not args.no_cpu_baseline and world == 1:
             out["cpu_baseline"] = cpu_baseline(w)
         print(json.dumps(out))

@@ -25,6 +25,8 @@
 // tensor memory), warps 4-11 element-wise math (warp % 4 = TMEM lane quarter, (warp-4)/4 = which 32 of the 64 block columns).
 #include <atomic>
 #include <mutex>
+#include <queue>
+#include <vector>
 
 #include "kernels.h"
 #include "tc_common.cuh"
@@ -459,6 +461,9 @@ struct DwArgs {
     float *ws;  // [nsplit][3][Hkuv][I][DH] fp32 partial sums
     int S, E, De, G, B, Hkuv;
     int tiles_per_seq, tiles_total, tiles_per_split;
+    // CTA -> (weight block, token-tile range).  Blocks [0, n_mixed) are split unevenly into a long part (launched first)
+    // and a short part of `small_tiles` tiles (launched last); the others into `nsplit` equal parts, part by part.
+    int nblk_j, n_blocks, nsplit, n_mixed, small_tiles;
     float s0, c;  // head_scaling; head_scaling * up_scaling * final_scaling
     WaitArgs wait;
 };
@@ -480,11 +485,25 @@ bwd_dw_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ C
     auto bar = [&](int i) { return sBar + 8u * i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int jblk = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
+    int blk, split, tile_begin, tile_end;
+    {
+        const int cta = blockIdx.x, n_even = args.n_blocks - args.n_mixed;
+        if (cta < args.n_mixed) {                               // long part of an unevenly split block
+            blk = cta; split = 0; tile_begin = 0; tile_end = args.tiles_total - args.small_tiles;
+        } else if (cta < args.n_mixed + n_even * args.nsplit) { // equal parts, part by part
+            const int r = cta - args.n_mixed;
+            split = r / n_even;
+            blk = args.n_mixed + (r - split * n_even);
+            tile_begin = split * args.tiles_per_split;
+            tile_end = min(tile_begin + args.tiles_per_split, args.tiles_total);
+        } else {                                                // short part of an unevenly split block
+            blk = cta - (args.n_mixed + n_even * args.nsplit); split = 1;
+            tile_begin = args.tiles_total - args.small_tiles; tile_end = args.tiles_total;
+        }
+    }
+    const int hk = blk / args.nblk_j, jblk = blk - hk * args.nblk_j;
     const int e = (jblk * kBI) / args.De;
-    const int tile_begin = split * args.tiles_per_split;
-    const int tile_end = min(tile_begin + args.tiles_per_split, args.tiles_total);
-    const int ntiles = tile_end - tile_begin;  // >= 1 by construction of the grid
+    const int ntiles = tile_end - tile_begin;  // >= 1 by construction of the plan
     const WaitCtl ctl{abort_flag, args.wait};
     constexpr int W = kKernelBwdDw * 100;
     // dV^T = sum_t dO^T A (d_h x 64, M = 128, N = 64) needs half the columns and three quarters of the tensor-pipe
@@ -815,16 +834,75 @@ int choose_nsplit(long long items, int tiles_total, int num_sms) {
 
 struct DwPlan {
     int tiles_per_seq, tiles_total, nsplit, tiles_per_split;
+    int n_mixed, small_tiles;   // uneven split of the first n_mixed blocks (two-way splits only), else 0
 };
+
+// Time at which the last of `jobs` (durations, in launch order) ends when each goes to the SM that frees up first.
+double list_schedule(const std::vector<double> &jobs, int num_sms) {
+    std::priority_queue<double, std::vector<double>, std::greater<double>> sm;
+    for (int i = 0; i < num_sms; ++i) sm.push(0.0);
+    double end = 0.0;
+    for (double j : jobs) {
+        const double t = sm.top() + j;
+        sm.pop();
+        sm.push(t);
+        if (t > end) end = t;
+    }
+    return end;
+}
+
+// With a two-way split the CTAs are equal and their last wave is partly empty (704 CTAs on 148 SMs: the fifth wave is
+// 76 % full, 5 % of the kernel).  Splitting some blocks unevenly -- long parts launched first, short parts last, the
+// equal halves of the other blocks in between -- lets the short parts fill the SMs the last wave would leave idle.
+// The split point and the number of such blocks are found by simulating the launch order for a few candidates; a CTA's
+// fixed cost (weights in, accumulators out) is taken as two token tiles.  The partial sums still number two per
+// block, so the reduction and the workspace do not change.
+void plan_uneven(DwPlan &p, long long items, int num_sms) {
+    p.n_mixed = p.small_tiles = 0;
+    if (p.nsplit != 2 || items > 2048 || p.tiles_total < 32) return;
+    const double ovh = 2.0;
+    const int T = p.tiles_total, half = p.tiles_per_split;
+    auto makespan = [&](int nmix, int small) {
+        std::vector<double> jobs;
+        jobs.reserve((size_t)(2 * items));
+        for (int i = 0; i < nmix; ++i) jobs.push_back(T - small + ovh);
+        for (long long i = 0; i < items - nmix; ++i) jobs.push_back(half + ovh);
+        for (long long i = 0; i < items - nmix; ++i) jobs.push_back(T - half + ovh);
+        for (int i = 0; i < nmix; ++i) jobs.push_back(small + ovh);
+        return list_schedule(jobs, num_sms);
+    };
+    const double base = makespan(0, 0);
+    double best = base;
+    const int step_small = T / 32 > 1 ? T / 32 : 1, step_mix = num_sms / 4 > 1 ? num_sms / 4 : 1;
+    for (int small = step_small; small < half; small += step_small)
+        for (int nmix = step_mix; nmix <= items; nmix += step_mix) {
+            const double m = makespan(nmix, small);
+            if (m < best - 1e-9) { best = m; p.n_mixed = nmix; p.small_tiles = small; }
+        }
+    if (best > 0.985 * base) p.n_mixed = p.small_tiles = 0;   // not worth a different launch order
+}
+
 DwPlan dw_plan(const flashmhf_dims &d, int num_sms) {
-    DwPlan p;
+    struct Key { long long items; int tiles_per_seq, tiles_total, num_sms; };
+    struct Entry { Key k; DwPlan p; };
+    static std::mutex mu;
+    static std::vector<Entry> cache;
     const int G = d.H / d.Hkuv;
-    p.tiles_per_seq = (d.S + kBT - 1) / kBT;
-    p.tiles_total = p.tiles_per_seq * G * d.B;
     const long long items = (long long)d.Hkuv * ((long long)d.E * d.De / kBI);
+    const Key key{items, (d.S + kBT - 1) / kBT, ((d.S + kBT - 1) / kBT) * G * d.B, num_sms};
+    std::lock_guard<std::mutex> lk(mu);
+    for (const Entry &e : cache)
+        if (e.k.items == key.items && e.k.tiles_per_seq == key.tiles_per_seq && e.k.tiles_total == key.tiles_total &&
+            e.k.num_sms == key.num_sms)
+            return e.p;
+    DwPlan p;
+    p.tiles_per_seq = key.tiles_per_seq;
+    p.tiles_total = key.tiles_total;
     const int ns = choose_nsplit(items, p.tiles_total, num_sms);
     p.tiles_per_split = (p.tiles_total + ns - 1) / ns;
     p.nsplit = (p.tiles_total + p.tiles_per_split - 1) / p.tiles_per_split;  // no empty split
+    plan_uneven(p, items, num_sms);
+    if (cache.size() < 256) cache.push_back(Entry{key, p});
     return p;
 }
 
@@ -866,8 +944,11 @@ int launch_bwd(const flashmhf_bwd_params &p, cudaStream_t st, int *n_launch) {
         const DwPlan pl = dw_plan(d, dc->num_sms);
         DwArgs wa{static_cast<const float *>(p.R.ptr), p.R.stride[0], p.R.stride[1], p.R.stride[2],
                   static_cast<float *>(p.workspace), d.S, d.E, d.De, G, d.B, d.Hkuv,
-                  pl.tiles_per_seq, pl.tiles_total, pl.tiles_per_split, s0, c, wait_args(dc)};
-        dim3 gw(d.E * d.De / kBI, d.Hkuv, pl.nsplit);
+                  pl.tiles_per_seq, pl.tiles_total, pl.tiles_per_split,
+                  d.E * d.De / kBI, d.Hkuv * (d.E * d.De / kBI), pl.nsplit, pl.n_mixed, pl.small_tiles, s0, c, wait_args(dc)};
+        const long long ctas = (long long)wa.n_blocks * pl.nsplit;
+        if (ctas > 0x7fffffffLL) return FLASHMHF_ERR_BAD_SHAPE;
+        dim3 gw((unsigned)ctas);
         prof_mark(st, kMarkStart);
         bwd_dw_kernel<DH><<<gw, kThreads, DwSmem<DH>::kTotal, st>>>(tmQ, tmdO, tmK, tmU, tmV, wa);
         prof_mark(st, kMarkBwdDw);

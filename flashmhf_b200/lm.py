@@ -79,10 +79,11 @@ class RMSNorm(nn.Module):
         return self.weight * x.to(dt)
 
 
-def rotary_tables(S, head_dim, theta, device, dtype):
-    """cos/sin [S, head_dim] as the reference builds them (fp32 angles, duplicated halves, cast to the activations' dtype)."""
+def rotary_tables(S, head_dim, theta, device, dtype, first=0):
+    """cos/sin [S, head_dim] of positions first .. first+S-1 as the reference builds them (fp32 angles, duplicated
+    halves, cast to the activations' dtype)."""
     inv_freq = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.int64, device=device).float() / head_dim))
-    ang = torch.arange(S, device=device).float()[:, None] * inv_freq[None, :]
+    ang = torch.arange(first, first + S, device=device).float()[:, None] * inv_freq[None, :]
     emb = torch.cat((ang, ang), dim=-1)
     return emb.cos().to(dtype), emb.sin().to(dtype)
 
@@ -121,7 +122,9 @@ class Attention(nn.Module):
         self.v_proj = nn.Linear(cfg.hidden_size, self.nkv * self.hd, bias=False)
         self.o_proj = nn.Linear(self.nh * self.hd, cfg.hidden_size, bias=False)
 
-    def forward(self, x, cos, sin):
+    def forward(self, x, cos, sin, kv_out=None):
+        """``kv_out``: optional (k_cache, v_cache) of one layer, [B, n_kv, T_max, hd]; the keys (rotated) and values of
+        the S positions are stored at [0, S) for later ``decode`` calls."""
         B, S, _ = x.shape
         q = self.q_proj(x).view(B, S, self.nh, self.hd)
         k = self.k_proj(x).view(B, S, self.nkv, self.hd)
@@ -133,8 +136,26 @@ class Attention(nn.Module):
             k = lm_ops.RotaryFunction.apply(k, ct, st).transpose(1, 2)
         else:
             q, k = _Rotary.apply(q.transpose(1, 2), cos, sin), _Rotary.apply(k.transpose(1, 2), cos, sin)
+        if kv_out is not None:
+            kv_out[0][:, :, :S].copy_(k)
+            kv_out[1][:, :, :S].copy_(v)
         o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.nkv != self.nh)
         return self.o_proj(o.transpose(1, 2).reshape(B, S, self.nh * self.hd))
+
+    def decode(self, x, cos_p, sin_p, k_cache, v_cache, pos):
+        """One new token per sequence: x [B,1,hidden] at position ``pos`` (a Python int: the same for every sequence),
+        rotary tables of that position [1, hd]; appends this token's key and value to the layer's cache at ``pos`` and
+        attends over positions [0, pos] (the cache update of modeling_mhffnmoe.py:568-571, as generation uses it)."""
+        B = x.shape[0]
+        q = self.q_proj(x).view(B, 1, self.nh, self.hd).transpose(1, 2)
+        k = self.k_proj(x).view(B, 1, self.nkv, self.hd).transpose(1, 2)
+        v = self.v_proj(x).view(B, 1, self.nkv, self.hd).transpose(1, 2)
+        q, k = _Rotary.apply(q, cos_p, sin_p), _Rotary.apply(k, cos_p, sin_p)
+        k_cache[:, :, pos:pos + 1].copy_(k)
+        v_cache[:, :, pos:pos + 1].copy_(v)
+        o = F.scaled_dot_product_attention(q, k_cache[:, :, :pos + 1], v_cache[:, :, :pos + 1], is_causal=False,
+                                           enable_gqa=self.nkv != self.nh)
+        return self.o_proj(o.transpose(1, 2).reshape(B, 1, self.nh * self.hd))
 
 
 class _HeadNorm(nn.Module):
@@ -182,8 +203,12 @@ class DecoderLayer(nn.Module):
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
 
-    def forward(self, h, cos, sin):
-        h = h + self.self_attn(self.input_layernorm(h), cos, sin)
+    def forward(self, h, cos, sin, kv_out=None):
+        h = h + self.self_attn(self.input_layernorm(h), cos, sin, kv_out)
+        return h + self.mlp(self.post_attention_layernorm(h))
+
+    def decode(self, h, cos_p, sin_p, k_cache, v_cache, pos):
+        h = h + self.self_attn.decode(self.input_layernorm(h), cos_p, sin_p, k_cache, v_cache, pos)
         return h + self.mlp(self.post_attention_layernorm(h))
 
 
@@ -193,6 +218,21 @@ class _Body(nn.Module):
         self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
         self.layers = nn.ModuleList(DecoderLayer(cfg, ffn) for _ in range(cfg.num_hidden_layers))
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+
+
+class KVCache:
+    """Keys (rotated) and values of every layer: two tensors [layers, B, n_kv, T_max, head_dim]."""
+
+    def __init__(self, cfg, batch, max_len, device, dtype=torch.bfloat16):
+        hd = cfg.hidden_size // cfg.num_attention_heads
+        shape = (cfg.num_hidden_layers, batch, cfg.num_key_value_heads, max_len, hd)
+        self.k = torch.zeros(shape, device=device, dtype=dtype)
+        self.v = torch.zeros(shape, device=device, dtype=dtype)
+
+    def nbytes(self, length):
+        """Bytes of keys and values a step that attends over ``length`` positions reads."""
+        L, B, n, _, hd = self.k.shape
+        return 2 * L * B * n * length * hd * self.k.element_size()
 
 
 class DecoderLM(nn.Module):
@@ -229,14 +269,25 @@ class DecoderLM(nn.Module):
                 p.copy_((torch.randn(p.shape, generator=g) * std).to(p.dtype))
         return self
 
-    def hidden(self, ids):
+    def hidden(self, ids, cache=None):
+        """``cache``: optional KVCache to fill with the keys and values of these positions (a prefill before decoding)."""
         B, S = ids.shape
         h = self.model.embed_tokens(ids)
         hd = self.cfg.hidden_size // self.cfg.num_attention_heads
         cos, sin = rotary_tables(S, hd, self.cfg.rope_theta, ids.device, h.dtype)
-        for layer in self.model.layers:
-            h = layer(h, cos, sin)
+        for i, layer in enumerate(self.model.layers):
+            h = layer(h, cos, sin, None if cache is None else (cache.k[i], cache.v[i]))
         return self.model.norm(h)
+
+    def decode_step(self, ids, cache, pos):
+        """ids [B,1], the token at position ``pos`` of every sequence; the cache holds positions [0, pos).  Returns the
+        logits [B, vocab] for position pos + 1 and leaves this token's keys and values in the cache."""
+        h = self.model.embed_tokens(ids)
+        hd = self.cfg.hidden_size // self.cfg.num_attention_heads
+        cos_p, sin_p = rotary_tables(1, hd, self.cfg.rope_theta, ids.device, h.dtype, first=pos)
+        for i, layer in enumerate(self.model.layers):
+            h = layer.decode(h, cos_p, sin_p, cache.k[i], cache.v[i], pos)
+        return self.lm_head(self.model.norm(h)[:, 0])
 
     def forward(self, ids):
         return self.lm_head(self.hidden(ids))

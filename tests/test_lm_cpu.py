@@ -56,6 +56,24 @@ def test_lm_matches_reference_modules_fp32():
             assert orc.rel_l2(grads[k[2:]].grad, torch.from_numpy(z[k])) < 2e-5, k
 
 
+def test_decode_steps_with_a_kv_cache_equal_the_full_forward():
+    """Prefill of the first 20 positions into a cache, then four single-token steps: each step's logits are the full
+    forward's logits at that position (fp32, oracle FFN), and the cache ends up holding what a longer prefill stores."""
+    m, ids = tiny_model()
+    with torch.no_grad():
+        full = m(ids)
+        cache = lm.KVCache(m.cfg, ids.shape[0], 32, "cpu", torch.float32)
+        m.hidden(ids[:, :20], cache)
+        for pos in range(20, 24):
+            logits = m.decode_step(ids[:, pos:pos + 1], cache, pos)
+            assert (logits - full[:, pos]).abs().max() < 2e-5
+        ref = lm.KVCache(m.cfg, ids.shape[0], 32, "cpu", torch.float32)
+        m.hidden(ids, ref)
+    assert (cache.k - ref.k).abs().max() < 1e-5 and (cache.v - ref.v).abs().max() < 1e-5
+    assert cache.nbytes(24) == 2 * m.cfg.num_hidden_layers * 2 * m.cfg.num_key_value_heads * 24 * \
+        (m.cfg.hidden_size // m.cfg.num_attention_heads) * 4
+
+
 def test_flops_and_param_count_of_the_370m_config():
     cfg = lm.LMConfig.lm_370m()
     with torch.device("meta"):

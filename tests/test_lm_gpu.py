@@ -58,3 +58,31 @@ def test_training_steps_reduce_the_loss_at_370m_layer_dims():
     assert losses[-1] < losses[0] - 0.5, losses
     assert all(np.isfinite(losses))
 
+
+
+def test_decode_steps_with_a_kv_cache_on_the_gpu():
+    """bf16 on the GPU with the CUDA FFN layer (its decode-shaped, split forward): a prefill into the cache followed by
+    single-token steps gives the full forward's logits at those positions, eagerly and replayed from a CUDA graph."""
+    m, ids = tiny_model()
+    c = _cuda_copy(m)
+    ids = ids.cuda()
+    with torch.no_grad():
+        full = c(ids).float()
+        cache = lm.KVCache(c.cfg, ids.shape[0], 32, "cuda")
+        c.hidden(ids[:, :20], cache)
+        for pos in range(20, 24):
+            logits = c.decode_step(ids[:, pos:pos + 1], cache, pos).float()
+            assert orc.rel_l2(logits, full[:, pos]) < 3e-2, pos
+        # the last step once more from a graph (a fixed position per captured step, as the bench replays it)
+        tok = ids[:, 23:24].clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            c.decode_step(tok, cache, 23)
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = c.decode_step(tok, cache, 23)
+        g.replay()
+        torch.cuda.synchronize()
+        assert orc.rel_l2(out.float(), full[:, 23]) < 3e-2
