@@ -5,6 +5,23 @@ import numpy as np
 import torch
 
 GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+REPO_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def find_reference_checkout():
+    """A checkout of the reference project on this machine, or None: the FLASHMHF_REFERENCE environment variable, an
+    install under baseline/_ref, or the `reference_path` the repository's BASELINE.json names."""
+    import json
+    cands = [os.environ.get("FLASHMHF_REFERENCE", ""), os.path.join(REPO_ROOT, "baseline", "_ref")]
+    try:
+        with open(os.path.join(REPO_ROOT, "BASELINE.json")) as f:
+            cands.append(json.load(f).get("reference_path", ""))
+    except (OSError, ValueError):
+        pass
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "models", "flashmhf", "modeling_mhffnmoe.py")):
+            return c
+    return None
 
 
 def load_golden(name):

@@ -116,9 +116,8 @@ def test_unmodified_reference_layer_picks_up_the_seam_module():
     resolve to this package's module.  Needs a checkout of the reference; skipped where there is none."""
     import flashmhf_b200
     from tests.golden.make_golden import load_reference
-    ref_root = next((p for p in (os.environ.get("FLASHMHF_REFERENCE", ""), "/root/reference",
-                                 os.path.join(ROOT, "baseline", "_ref"))
-                     if p and os.path.exists(os.path.join(p, "models", "flashmhf", "modeling_mhffnmoe.py"))), None)
+    from tests.golden_util import find_reference_checkout
+    ref_root = find_reference_checkout()
     if ref_root is None:
         pytest.skip("no reference checkout on this machine")
     seam = flashmhf_b200.install_reference_seam()

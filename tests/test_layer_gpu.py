@@ -70,9 +70,8 @@ def test_unmodified_reference_layer_runs_the_cuda_operator_through_its_import_se
     import os
     import flashmhf_b200
     from tests.golden.make_golden import load_reference, seeded_params
-    ref_root = next((p for p in (os.environ.get("FLASHMHF_REFERENCE", ""), "/root/reference",
-                                 os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref"))
-                     if p and os.path.exists(os.path.join(p, "models", "flashmhf", "modeling_mhffnmoe.py"))), None)
+    from tests.golden_util import find_reference_checkout
+    ref_root = find_reference_checkout()
     if ref_root is None:
         pytest.skip("no reference checkout on this machine")
     flashmhf_b200.install_reference_seam()
