@@ -331,18 +331,31 @@ def lm_train_370m(args, rank, world, dev, sync_all):
 def lm_inference(name, cfg, rows, seq, what, args, rank, world, dev, sync_all):
     """Token-sharded inference: the batch rows of one request (`rows` x `seq` uniform random token ids, the same on every
     N) are split over the ranks with dp.shard_range; weights are replicated; no collective in the data path (attention
-    stays inside a sequence, the FFN has no cross-token dependence).  Each timed step copies this rank's ids from pinned
+    stays inside a sequence, the FFN has no cross-token dependence).  A prefill on more ranks than sequences also cuts
+    the sequences into consecutive parts (see below: the one case with an exchange, keys and values from part to part).  Each timed step copies this rank's ids from pinned
     host memory, runs the bf16 forward and reads the arg-max of the last position's logits back.  `what` = "logits"
     (full forward, logits at every position) or "prefill" (hidden states everywhere, logits of the last position).
     Reports whole-job tokens/s from the slowest rank's time."""
     from flashmhf_b200 import _lib, dp, lm
     a, b = dp.shard_range(rows, rank, world) if rank < min(world, rows) else (0, 0)
-    if world > rows:                                   # more ranks than rows: the first `rows` ranks take one row each
-        a, b = (rank, rank + 1) if rank < rows else (0, 0)
+    parts, link, t_a, t_b = 1, None, 0, seq
+    if world > rows:
+        if what == "prefill" and world % rows == 0 and seq % (world // rows) == 0:
+            # More ranks than sequences: every sequence is cut into world/rows consecutive parts, one per rank.  The FFN,
+            # the projections and the norms are position-wise; attention needs the earlier parts' keys and values, which
+            # travel from part to part once per layer (NCCL send/recv between the ranks of one sequence).
+            parts = world // rows
+            row, part = rank // parts, rank % parts
+            a, b = row, row + 1
+            t_a, t_b = part * (seq // parts), (part + 1) * (seq // parts)
+            link = lm.SequenceLink(first=t_a, recv_from=rank - 1 if part > 0 else None,
+                                   send_to=rank + 1 if part + 1 < parts else None)
+        else:                                          # the first `rows` ranks take one row each, the others have no work
+            a, b = (rank, rank + 1) if rank < rows else (0, 0)
     with torch.device(dev):
         model = lm.DecoderLM(cfg).to(torch.bfloat16).init_weights(seed=0)
     ids_all = torch.randint(0, cfg.vocab_size, (rows, seq), generator=torch.Generator().manual_seed(0))
-    ids_host = ids_all[a:b].contiguous().pin_memory() if b > a else None
+    ids_host = ids_all[a:b, t_a:t_b].contiguous().pin_memory() if b > a else None
     out_host = torch.zeros(max(1, b - a), dtype=torch.int64).pin_memory()
 
     ids_dev = ids_host.to(dev) if ids_host is not None else None   # static device buffer the captured graph reads
@@ -352,7 +365,7 @@ def lm_inference(name, cfg, rows, seq, what, args, rank, world, dev, sync_all):
         if what == "logits":
             last = model(ids_dev)[:, -1]
         else:
-            last = model.lm_head(model.hidden(ids_dev)[:, -1])
+            last = model.lm_head(model.hidden(ids_dev, link=link)[:, -1])   # (the request's answer is the last part's)
         return last.float().argmax(-1)
 
     # The forward pass of a small model is hundreds of short kernels: replayed from a CUDA graph so that the step is
@@ -366,12 +379,15 @@ def lm_inference(name, cfg, rows, seq, what, args, rank, world, dev, sync_all):
         result = forward()
         ffn_ms = sum(sum(v) for v in _lib.profile_end(capacity=16 * cfg.num_hidden_layers + 16).values())
         try:
+            if link is not None:
+                raise RuntimeError("a split sequence exchanges keys and values between ranks: run eagerly")
             g_ = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g_):
                 result = forward()
             graph = g_
         except Exception as e:   # capture is an optimisation of the harness, not a requirement
-            print(f"bench: {name} inference runs without a CUDA graph ({type(e).__name__}: {e})", file=sys.stderr)
+            if link is None:
+                print(f"bench: {name} inference runs without a CUDA graph ({type(e).__name__}: {e})", file=sys.stderr)
             torch.cuda.synchronize()
 
     def step():
@@ -404,10 +420,12 @@ def lm_inference(name, cfg, rows, seq, what, args, rank, world, dev, sync_all):
     return {"model": name, "pass": "bf16 forward, " + ("logits at every position" if what == "logits" else
                                                         "prefill: hidden states of all tokens, logits of the last"),
             "rows": rows, "seq_len": seq, "tokens_per_s": rows * seq / (ms * 1e-3), "ms_per_step": ms, "steps": n, "warmup": 2,
-            "split": f"batch rows over {min(world, rows)} of {world} ranks, no collective in the data path",
+            "split": (f"batch rows over {min(world, rows)} of {world} ranks, no collective in the data path" if parts == 1 else
+                      f"{rows} sequences x {parts} consecutive parts of {seq // parts} tokens over {world} ranks; keys and values "
+                      "pass from part to part once per layer (NCCL send/recv), nothing else is exchanged"),
             "cuda_graph": graph is not None,
-            "ranks_with_work": min(world, rows), "ffn_kernels_share": share,
-            "h2d_bytes_per_step_per_rank": (b - a) * seq * 8, "d2h_bytes_per_step_per_rank": (b - a) * 8}
+            "ranks_with_work": min(world, rows) * parts, "ffn_kernels_share": share,
+            "h2d_bytes_per_step_per_rank": (b - a) * (t_b - t_a) * 8, "d2h_bytes_per_step_per_rank": (b - a) * 8}
 
 
 def lm_decode(name, cfg, rows, context, args, rank, world, dev, sync_all):
@@ -509,6 +527,7 @@ def main():
     ap.add_argument("--no-lm", action="store_true", help="skip the LM measurements (370M training step, inference runs)")
     ap.add_argument("--lm-steps", type=int, default=8)
     ap.add_argument("--infer-steps", type=int, default=10)
+    ap.add_argument("--prefill-rows", type=int, default=4, help="sequences of the 1.3B prefill request (4 in the headline configuration)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -652,7 +671,7 @@ def main():
         train = lm_train_370m(args, rank, world, dev, sync_all)
         torch.cuda.empty_cache()
         infer = lm_inference("128M", lm.LMConfig.lm_128m(), 8, 2048, "logits", args, rank, world, dev, sync_all)
-        prefill = lm_inference("1.3B", lm.LMConfig.lm_1p3b(), 4, 8192, "prefill", args, rank, world, dev, sync_all)
+        prefill = lm_inference("1.3B", lm.LMConfig.lm_1p3b(), args.prefill_rows, 8192, "prefill", args, rank, world, dev, sync_all)
         decode = lm_decode("1.3B", lm.LMConfig.lm_1p3b(), 64, 4096, args, rank, world, dev, sync_all)
 
     if rank == 0:

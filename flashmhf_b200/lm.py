@@ -112,6 +112,26 @@ class _Rotary(torch.autograd.Function):
         return dx, None, None
 
 
+def _attend_with_prefix(q, kp, vp, k, v, gqa):
+    """Attention of S queries over P earlier positions (kp, vp: all visible) followed by their own S positions (k, v:
+    causal).  On a GPU, as two calls of the library attention that return their log-sum-exp, merged exactly
+    (o = o1 e^(l1-l) + o2 e^(l2-l), l = log(e^l1 + e^l2)): its causal kernel on the square part is several times faster
+    than a masked call over the rectangle.  Elsewhere (CPU, grouped K/V heads) one call with a causal mask aligned to the
+    lower right corner."""
+    if q.is_cuda and not gqa and q.dtype in (torch.bfloat16, torch.float16):
+        try:
+            op = torch.ops.aten._scaled_dot_product_cudnn_attention
+            o1, l1 = op(q, kp, vp, None, True, 0.0, False, False)[:2]
+            o2, l2 = op(q, k, v, None, True, 0.0, True, False)[:2]
+            l = torch.logaddexp(l1, l2)
+            return (o1.float() * (l1 - l).exp() + o2.float() * (l2 - l).exp()).to(q.dtype)
+        except (RuntimeError, AttributeError, TypeError):
+            pass   # this build of torch has no such kernel for these shapes: the masked call below
+    from torch.nn.attention.bias import causal_lower_right
+    kk, vv = torch.cat((kp, k), dim=2), torch.cat((vp, v), dim=2)
+    return F.scaled_dot_product_attention(q, kk, vv, attn_mask=causal_lower_right(q.shape[2], kk.shape[2]), enable_gqa=gqa)
+
+
 class Attention(nn.Module):
     def __init__(self, cfg):
         super().__init__()
@@ -122,9 +142,11 @@ class Attention(nn.Module):
         self.v_proj = nn.Linear(cfg.hidden_size, self.nkv * self.hd, bias=False)
         self.o_proj = nn.Linear(self.nh * self.hd, cfg.hidden_size, bias=False)
 
-    def forward(self, x, cos, sin, kv_out=None):
+    def forward(self, x, cos, sin, kv_out=None, link=None):
         """``kv_out``: optional (k_cache, v_cache) of one layer, [B, n_kv, T_max, hd]; the keys (rotated) and values of
-        the S positions are stored at [0, S) for later ``decode`` calls."""
+        the S positions are stored at [0, S) for later ``decode`` calls.
+        ``link``: optional SequenceLink when a sequence is split over two ranks: the rank with the earlier part sends
+        its keys and values on, the rank with the later part receives them and attends over both parts."""
         B, S, _ = x.shape
         q = self.q_proj(x).view(B, S, self.nh, self.hd)
         k = self.k_proj(x).view(B, S, self.nkv, self.hd)
@@ -139,7 +161,15 @@ class Attention(nn.Module):
         if kv_out is not None:
             kv_out[0][:, :, :S].copy_(k)
             kv_out[1][:, :, :S].copy_(v)
-        o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.nkv != self.nh)
+        if link is not None and link.recv_from is not None:
+            kp, vp = link.receive()
+            if link.send_to is not None:
+                link.send(torch.cat((kp, k), dim=2), torch.cat((vp, v), dim=2))
+            o = _attend_with_prefix(q, kp, vp, k, v, self.nkv != self.nh)
+        else:
+            if link is not None and link.send_to is not None:
+                link.send(k, v)
+            o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.nkv != self.nh)
         return self.o_proj(o.transpose(1, 2).reshape(B, S, self.nh * self.hd))
 
     def decode(self, x, cos_p, sin_p, k_cache, v_cache, pos):
@@ -203,8 +233,8 @@ class DecoderLayer(nn.Module):
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
 
-    def forward(self, h, cos, sin, kv_out=None):
-        h = h + self.self_attn(self.input_layernorm(h), cos, sin, kv_out)
+    def forward(self, h, cos, sin, kv_out=None, link=None):
+        h = h + self.self_attn(self.input_layernorm(h), cos, sin, kv_out, link)
         return h + self.mlp(self.post_attention_layernorm(h))
 
     def decode(self, h, cos_p, sin_p, k_cache, v_cache, pos):
@@ -218,6 +248,53 @@ class _Body(nn.Module):
         self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
         self.layers = nn.ModuleList(DecoderLayer(cfg, ffn) for _ in range(cfg.num_hidden_layers))
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps)
+
+
+class SequenceLink:
+    """One rank's place in a sequence that is split into consecutive parts over ranks (a prefill on more GPUs than
+    there are sequences).  Per layer, the rank of part p receives the keys and values of positions [0, first) from the
+    rank of part p-1 and, unless it holds the last part, sends those of [0, first + S) on to the rank of part p+1 --
+    point-to-point messages (NCCL send/recv on GPUs), the one exchange this split needs: the FFN, the projections and
+    the norms are position-wise, and attention needs the earlier positions' keys and values only.  All receives of a
+    forward pass are posted when it starts and the sends are not waited for until it ends, so the messages of later
+    layers travel while earlier layers compute."""
+
+    def __init__(self, first, recv_from=None, send_to=None, group=None):
+        self.first, self.recv_from, self.send_to, self.group = first, recv_from, send_to, group
+        self._recv, self._sent, self._layer = [], [], 0
+
+    def start(self, cfg, batch, device, dtype):
+        """Called by DecoderLM.hidden before the first layer."""
+        import torch.distributed as dist
+        self._recv, self._sent, self._layer = [], [], 0
+        if self.recv_from is None:
+            return
+        hd = cfg.hidden_size // cfg.num_attention_heads
+        for _ in range(cfg.num_hidden_layers):
+            kp = torch.empty((batch, cfg.num_key_value_heads, self.first, hd), device=device, dtype=dtype)
+            vp = torch.empty_like(kp)
+            self._recv.append((kp, vp, dist.irecv(kp, self.recv_from, group=self.group),
+                               dist.irecv(vp, self.recv_from, group=self.group)))
+
+    def send(self, k, v):
+        import torch.distributed as dist
+        k, v = k.contiguous(), v.contiguous()
+        self._sent.append((k, v, dist.isend(k, self.send_to, group=self.group), dist.isend(v, self.send_to, group=self.group)))
+
+    def receive(self):
+        """Keys and values of the earlier positions for the layer now running (layers call in order)."""
+        kp, vp, wk, wv = self._recv[self._layer]
+        self._layer += 1
+        wk.wait()
+        wv.wait()
+        return kp, vp
+
+    def finish(self):
+        """Called by DecoderLM.hidden after the last layer: the sent tensors may be released once their sends are done."""
+        for _, _, wk, wv in self._sent:
+            wk.wait()
+            wv.wait()
+        self._recv, self._sent = [], []
 
 
 class KVCache:
@@ -269,14 +346,20 @@ class DecoderLM(nn.Module):
                 p.copy_((torch.randn(p.shape, generator=g) * std).to(p.dtype))
         return self
 
-    def hidden(self, ids, cache=None):
-        """``cache``: optional KVCache to fill with the keys and values of these positions (a prefill before decoding)."""
+    def hidden(self, ids, cache=None, link=None):
+        """``cache``: optional KVCache to fill with the keys and values of these positions (a prefill before decoding).
+        ``link``: optional SequenceLink: ``ids`` are then the positions [link.first, link.first + S) of longer sequences
+        whose other parts other ranks hold (everything but attention is position-wise)."""
         B, S = ids.shape
         h = self.model.embed_tokens(ids)
         hd = self.cfg.hidden_size // self.cfg.num_attention_heads
-        cos, sin = rotary_tables(S, hd, self.cfg.rope_theta, ids.device, h.dtype)
+        cos, sin = rotary_tables(S, hd, self.cfg.rope_theta, ids.device, h.dtype, first=0 if link is None else link.first)
+        if link is not None:
+            link.start(self.cfg, B, ids.device, h.dtype)
         for i, layer in enumerate(self.model.layers):
-            h = layer(h, cos, sin, None if cache is None else (cache.k[i], cache.v[i]))
+            h = layer(h, cos, sin, None if cache is None else (cache.k[i], cache.v[i]), link)
+        if link is not None:
+            link.finish()
         return self.model.norm(h)
 
     def decode_step(self, ids, cache, pos):

@@ -134,3 +134,39 @@ def test_grad_reducer_single_process_is_a_no_op():
     assert red.world == 1 and not red._hooks
     lm.train_step(m, torch.optim.SGD(m.parameters(), lr=0.0), ids, red)
     assert all(p.grad is not None for p in m.parameters())
+
+
+def _split_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        m, ids = tiny_model()
+        S = ids.shape[1]
+        a, b = dp.shard_range(S, rank, world)               # consecutive parts of every sequence
+        link = lm.SequenceLink(first=a, recv_from=rank - 1 if rank > 0 else None,
+                               send_to=rank + 1 if rank + 1 < world else None)
+        with torch.no_grad():
+            mine = m.hidden(ids[:, a:b], link=link)
+            full = m.hidden(ids)
+        out.put((rank, float((mine - full[:, a:b]).abs().max())))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_sequence_split_prefill_world3_equals_the_full_forward():
+    """Every sequence cut into three consecutive parts, one per gloo rank: keys and values travel from part to part,
+    each rank's hidden states are the full forward's at its positions (fp32, oracle FFN)."""
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_split_worker, args=(r, 3, port, out)) for r in range(3)]
+    for p in procs:
+        p.start()
+    res = [out.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    for rank, err in res:
+        assert err < 2e-5, (rank, err)
