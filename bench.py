@@ -338,7 +338,7 @@ def lm_inference(name, cfg, rows, seq, what, args, rank, world, dev, sync_all):
     Reports whole-job tokens/s from the slowest rank's time."""
     from flashmhf_b200 import _lib, dp, lm
     a, b = dp.shard_range(rows, rank, world) if rank < min(world, rows) else (0, 0)
-    parts, link, t_a, t_b = 1, None, 0, seq
+    parts, link, t_a, t_b, cuts = 1, None, 0, seq, [0, seq]
     if world > rows:
         if what == "prefill" and world % rows == 0 and seq % (world // rows) == 0:
             # More ranks than sequences: every sequence is cut into world/rows consecutive parts, one per rank.  The FFN,
@@ -347,7 +347,12 @@ def lm_inference(name, cfg, rows, seq, what, args, rank, world, dev, sync_all):
             parts = world // rows
             row, part = rank // parts, rank % parts
             a, b = row, row + 1
-            t_a, t_b = part * (seq // parts), (part + 1) * (seq // parts)
+            # Equal parts, except for two: the later part attends over the earlier one as well, so the earlier part is made
+            # longer (9/16 of the sequence balances the two at this model's ratio of attention to position-wise work).
+            cuts = [p_ * (seq // parts) for p_ in range(parts)] + [seq]
+            if parts == 2 and seq % 2048 == 0:
+                cuts[1] = seq * 9 // 16
+            t_a, t_b = cuts[part], cuts[part + 1]
             link = lm.SequenceLink(first=t_a, recv_from=rank - 1 if part > 0 else None,
                                    send_to=rank + 1 if part + 1 < parts else None)
         else:                                          # the first `rows` ranks take one row each, the others have no work
@@ -417,12 +422,16 @@ def lm_inference(name, cfg, rows, seq, what, args, rank, world, dev, sync_all):
     share = dp.max_over_ranks(ffn_ms / mine if ids_host is not None and mine > 0 else 0.0, dev)
     del model
     torch.cuda.empty_cache()
+    if parts == 1:
+        split_note = f"batch rows over {min(world, rows)} of {world} ranks, no collective in the data path"
+    else:
+        sizes = " + ".join(str(cuts[i + 1] - cuts[i]) for i in range(parts))
+        split_note = (f"{rows} sequences x {parts} consecutive parts ({sizes} tokens) over {world} ranks; keys and values pass "
+                      "from part to part once per layer (NCCL send/recv), nothing else is exchanged")
     return {"model": name, "pass": "bf16 forward, " + ("logits at every position" if what == "logits" else
                                                         "prefill: hidden states of all tokens, logits of the last"),
             "rows": rows, "seq_len": seq, "tokens_per_s": rows * seq / (ms * 1e-3), "ms_per_step": ms, "steps": n, "warmup": 2,
-            "split": (f"batch rows over {min(world, rows)} of {world} ranks, no collective in the data path" if parts == 1 else
-                      f"{rows} sequences x {parts} consecutive parts of {seq // parts} tokens over {world} ranks; keys and values "
-                      "pass from part to part once per layer (NCCL send/recv), nothing else is exchanged"),
+            "split": split_note,
             "cuda_graph": graph is not None,
             "ranks_with_work": min(world, rows) * parts, "ffn_kernels_share": share,
             "h2d_bytes_per_step_per_rank": (b - a) * (t_b - t_a) * 8, "d2h_bytes_per_step_per_rank": (b - a) * 8}
