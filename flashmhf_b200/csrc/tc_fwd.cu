@@ -40,7 +40,6 @@ namespace {
 
 constexpr int kBT = 128;  // token rows per tile
 constexpr int kBI = 64;   // intermediate rows per block
-constexpr int kSBufs = 2;   // S buffers in tensor memory
 // Shared-memory stages of the [K;U] ring and of the V ring (two Q tiles take the rest).  The [K;U] ring must have an
 // EVEN number of stages: its "full" barriers are waited on by the two S issuers, which own alternate blocks, and a
 // barrier's phase is tracked with one parity bit, so each stage must always be waited on by the same issuer (with an
